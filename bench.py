@@ -1,0 +1,224 @@
+#!/usr/bin/env python
+"""Headline benchmark: rating updates/s of matrix-factorisation SGD.
+
+Config (synthetic, seeded): 1,000,000 users x 200,000 items, 200 M (user, item)
+pairs drawn Zipf(1.1), ratings round(clip(p.q + N(0, 0.5), 1, 5)) from rank-16
+latents; model rank 128 fp32, lr 0.005, L2 0.02, SSP staleness 2.  The total
+work is fixed, so the scaling over GPUs is strong scaling.
+
+One step = one training round of the public API (`MfSgdGpu.round`): SSP wait +
+pull of the local rows from the HBM shards, one SGD pass over all local
+ratings, push of the weighted deltas to the owners, clock commit.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 5 --warmup 3
+
+Rank 0 prints one JSON line.  `value` is device-timed (CUDA events, max over
+ranks) with the ratings resident in HBM; `e2e` repeats the measurement with the
+ratings streamed from pinned host memory every round and the round's running
+RMSE read back to the host.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+REF_UNAVAILABLE = ("the reference is a CMake C++11 project with no Python packaging "
+                   "(pip: 'neither setup.py nor pyproject.toml found') and needs MPI, ZeroMQ, "
+                   "msgpack-c, Boost, Eigen3, gflags and glog, none of which exist on this image")
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_torch"])
+    ap.add_argument("--users", type=int, default=1_000_000)
+    ap.add_argument("--items", type=int, default=200_000)
+    ap.add_argument("--nnz", type=int, default=200_000_000)
+    ap.add_argument("--rank", type=int, default=128)
+    ap.add_argument("--alpha", type=float, default=0.005)
+    ap.add_argument("--beta", type=float, default=0.02)
+    ap.add_argument("--staleness", type=int, default=2)
+    ap.add_argument("--seed", type=int, default=20240611)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-balance", action="store_true")
+    ap.add_argument("--hot-mix", type=float, default=1.0)
+    ap.add_argument("--sgd-blocks", type=int, default=0)
+    return ap.parse_args()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if rank == 0:
+            print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch with torchrun",
+                  file=sys.stderr)
+        return 2
+    if not torch.cuda.is_available():
+        print("bench.py needs a CUDA device", file=sys.stderr)
+        return 2
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world,
+                                device_id=dev)
+
+    from paracel_b200.ops import _lib
+    from paracel_b200.utils.clocks import ClockSampler
+    from paracel_b200.utils.synth import MfRatingStream
+
+    if args.impl == "nccl_torch":
+        from paracel_b200.baselines.mf_nccl_torch import MfSgdNcclTorch as Model
+    else:
+        from paracel_b200.models.mf_gpu import MfSgdGpu as Model
+    from paracel_b200.models.mf_gpu import balanced_groups
+
+    K, Wm = args.steps, args.warmup
+    total_rounds = 2 * (K + Wm) + 4
+    t_setup = time.time()
+    model = Model(args.users, args.items, k=args.rank, alpha=args.alpha, beta=args.beta,
+                  rounds=total_rounds, staleness=args.staleness, ssp=True, seed=args.seed,
+                  hot_mix=args.hot_mix, sgd_blocks=args.sgd_blocks, device=dev)
+
+    # ---- data: every rank regenerates the same global stream and keeps its block
+    stream = MfRatingStream(args.users, args.items, args.nnz, seed=args.seed, device=dev)
+    if world > 1 and not args.no_balance:
+        cu, ci = stream.counts()
+        ugrp = balanced_groups(cu, model.npx)
+        igrp = balanced_groups(ci, model.npy)
+    else:
+        ar_u = torch.arange(args.users, device=dev)
+        ar_i = torch.arange(args.items, device=dev)
+        ugrp = (ar_u % model.npx).to(torch.int32)
+        igrp = (ar_i % model.npy).to(torch.int32)
+    us, is_, rs = [], [], []
+    for u, i, r in stream:
+        if world > 1:
+            keep = (ugrp[u].to(torch.int64) * model.npy + igrp[i].to(torch.int64)) == rank
+            u, i, r = u[keep], i[keep], r[keep]
+        us.append(u.to(torch.int32))
+        is_.append(i.to(torch.int32))
+        rs.append(r.to(torch.float16))
+    u = torch.cat(us).to(torch.int64)
+    i = torch.cat(is_).to(torch.int64)
+    r = torch.cat(rs).to(torch.float32)
+    del us, is_, rs, stream
+    local_nnz = u.numel()
+    model.load_ratings(u, i, r)
+    del u, i, r
+    torch.cuda.empty_cache()
+    model.init_parameters()
+    t_setup = time.time() - t_setup
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(n_steps, read_result):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = _lib.launches()
+        e0.record()
+        last = None
+        for _ in range(n_steps):
+            model.round()
+            if read_result:
+                last = float(model.sse.item())  # device -> host read of the step's result
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        barrier()
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), _lib.launches() - l0, last
+
+    # ---- device-timed: ratings resident in HBM
+    for _ in range(Wm):
+        model.round()
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    ms, launches, _ = timed(K, False)
+    clocks = sampler.stop() if sampler else None
+    model.clock.check()
+    run_rmse = model.running_rmse()
+    value = args.nnz * K / (ms * 1e-3)
+
+    # ---- end to end: ratings streamed from pinned host memory each round
+    e2e = None
+    if not args.no_e2e and hasattr(model, "offload_ratings"):
+        model.offload_ratings()
+        for _ in range(Wm):
+            model.round()
+            float(model.sse.item())
+        ms2, _, last = timed(K, True)
+        model.clock.check()
+        e2e = {"value": args.nnz * K / (ms2 * 1e-3), "unit": "rating updates/s",
+               "ms_per_step": ms2 / K,
+               "h2d_bytes_per_step": int(model.h2d_bytes), "d2h_bytes_per_step": 8}
+    final_rmse = model.running_rmse()
+
+    mx = torch.tensor([local_nnz], dtype=torch.int64, device=dev)
+    mn = mx.clone()
+    if world > 1:
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        out = {
+            "metric": "rating updates/s (MF-SGD)",
+            "value": value,
+            "unit": "rating updates/s",
+            "n_gpus": world,
+            "steps": K,
+            "warmup": Wm,
+            "ms_per_step": ms / K,
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "fp32",
+            "data": "synthetic (seeded Zipf(1.1) pairs, rank-16 latent ratings), random-init factors",
+            "impl": args.impl,
+            "config": {
+                "model": "biased MF, SGD, rank %d fp32" % args.rank,
+                "users": args.users, "items": args.items, "ratings": args.nnz,
+                "global_batch": args.nnz, "seq_len": None,
+                "lr": args.alpha, "l2": args.beta, "ssp_staleness": args.staleness,
+                "parallelism": "ps-shards-in-hbm x fsmap %dx%d" % (model.npx, model.npy),
+                "l2_policy": "inputs larger than L2: %.0f MB of ratings per rank and %.0f MB of "
+                             "factor rows are streamed every step"
+                             % (local_nnz * 12 / 1e6, (args.users + args.items) * model.D * 4 / 1e6 / world),
+                "ratings_per_rank_max": int(mx.item()), "ratings_per_rank_min": int(mn.item()),
+            },
+            "clocks": clocks,
+            "e2e": e2e,
+            "gpu_launches": launches,
+            "running_rmse_device_phase": run_rmse,
+            "running_rmse_final": final_rmse,
+            "setup_s": t_setup,
+        }
+        print(json.dumps(out))
+    model.free()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

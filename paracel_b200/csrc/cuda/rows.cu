@@ -1,0 +1,282 @@
+// Sparse keyed pull / push of fixed-width rows against a table that is sharded
+// over the HBM of all ranks (row g lives on rank g % world at local row
+// g / world).  This is the device replacement of paracel_read_multi /
+// paracel_bupdate_multi (reference: include/ps.hpp:482-534, 810-871 and the
+// per-row loops of alg/recommendation/matrix_factorization/mf.hpp:202-262):
+// the all-to-all "dispatch" is the address computation, the row gather is a
+// 128-bit peer load over NVLink, and the "combine" is a vector reduction issued
+// straight into the owner's shard, where the registered handler (add / scaled
+// add / max) is applied by the L2 atomic unit of the owner GPU.
+//
+// The pull kernel can also carry the SSP staleness wait (bounded spin on the
+// clock words that peers store into this GPU's memory), so that "wait until
+// nobody is more than s clocks behind, then read" is one launch.
+#include "common.cuh"
+
+namespace {
+
+enum Handler { H_ADD = 0, H_SCALED_ADD = 1, H_MAX = 2 };
+
+struct PullArgs {
+  const long long* ids;      // n global row ids
+  float* const* shards;      // world pointers (device array)
+  int world;
+  int D;                     // floats per row, multiple of 4
+  long long n;
+  float* dst;                // n x D working copy
+  float* dst0;               // n x D snapshot (may be null)
+  const long long* clocks;   // SSP clocks in local memory (may be null)
+  long long target;          // wait for min(clocks) >= target (<=0: no wait)
+  unsigned long long timeout_ns;
+  PclStatus* status;
+  int rank;
+};
+
+__global__ void __launch_bounds__(256) rows_pull_kernel(PullArgs a) {
+  __shared__ int ok;
+  if (a.clocks != nullptr && a.target > 0) {
+    if (threadIdx.x == 0)
+      ok = pcl_wait_min_clock(a.clocks, a.world, a.target, a.timeout_ns, a.status, a.rank, 1)
+               ? 1 : 0;
+    __syncthreads();
+    if (!ok) return;
+  }
+  const int vec_per_row = a.D >> 2;
+  // threads per row: largest power of two <= min(32, vec_per_row)
+  int tpr = 32;
+  while (tpr > vec_per_row) tpr >>= 1;
+  const int rows_per_block = blockDim.x / tpr;
+  const int sub = threadIdx.x % tpr;
+  const int rib = threadIdx.x / tpr;
+  for (long long row = (long long)blockIdx.x * rows_per_block + rib; row < a.n;
+       row += (long long)gridDim.x * rows_per_block) {
+    long long g = a.ids[row];
+    int owner = (int)(g % a.world);
+    long long lrow = g / a.world;
+    const float* src = a.shards[owner] + lrow * a.D;
+    float* d = a.dst + row * a.D;
+    float* d0 = a.dst0 ? a.dst0 + row * a.D : nullptr;
+    for (int v = sub; v < vec_per_row; v += tpr) {
+      float4 x = pcl_ld_sys4(src + 4 * v);
+      *reinterpret_cast<float4*>(d + 4 * v) = x;
+      if (d0) *reinterpret_cast<float4*>(d0 + 4 * v) = x;
+    }
+  }
+}
+
+struct PushArgs {
+  const long long* ids;
+  float* const* shards;
+  int world;
+  int D;
+  long long n;
+  float* cur;          // n x D current working copy
+  float* old;          // n x D snapshot taken at pull time; may be null (delta = cur)
+  const float* wgt;    // n per-row weights or null (=1)
+  float scale;         // extra scale for H_SCALED_ADD
+  int handler;
+  int refresh_old;     // write old = cur after pushing
+};
+
+__device__ __forceinline__ void atomic_max_f32(float* p, float v) {
+  // order-preserving integer trick; valid for non-NaN values
+  if (v >= 0.f) atomicMax(reinterpret_cast<int*>(p), __float_as_int(v));
+  else atomicMin(reinterpret_cast<unsigned int*>(p), __float_as_uint(v));
+}
+
+__global__ void __launch_bounds__(256) rows_push_kernel(PushArgs a) {
+  const int vec_per_row = a.D >> 2;
+  int tpr = 32;
+  while (tpr > vec_per_row) tpr >>= 1;
+  const int rows_per_block = blockDim.x / tpr;
+  const int sub = threadIdx.x % tpr;
+  const int rib = threadIdx.x / tpr;
+  for (long long row = (long long)blockIdx.x * rows_per_block + rib; row < a.n;
+       row += (long long)gridDim.x * rows_per_block) {
+    long long g = a.ids[row];
+    int owner = (int)(g % a.world);
+    long long lrow = g / a.world;
+    float* dstp = a.shards[owner] + lrow * a.D;
+    float w = a.wgt ? a.wgt[row] : 1.f;
+    if (a.handler == H_SCALED_ADD) w *= a.scale;
+    float* c = a.cur + row * a.D;
+    float* o = a.old ? a.old + row * a.D : nullptr;
+    for (int v = sub; v < vec_per_row; v += tpr) {
+      float4 x = *reinterpret_cast<const float4*>(c + 4 * v);
+      float4 d = x;
+      if (o) {
+        float4 y = *reinterpret_cast<const float4*>(o + 4 * v);
+        d.x -= y.x; d.y -= y.y; d.z -= y.z; d.w -= y.w;
+        if (a.refresh_old) *reinterpret_cast<float4*>(o + 4 * v) = x;
+      }
+      if (a.handler == H_MAX) {
+        atomic_max_f32(dstp + 4 * v + 0, x.x);
+        atomic_max_f32(dstp + 4 * v + 1, x.y);
+        atomic_max_f32(dstp + 4 * v + 2, x.z);
+        atomic_max_f32(dstp + 4 * v + 3, x.w);
+      } else {
+        d.x *= w; d.y *= w; d.z *= w; d.w *= w;
+        if (d.x != 0.f || d.y != 0.f || d.z != 0.f || d.w != 0.f)
+          pcl_red_add4_sys(dstp + 4 * v, d);
+      }
+    }
+  }
+}
+
+// Scalar tables (biases, counts): one element per id.
+struct ScalarArgs {
+  const long long* ids;
+  float* const* shards;
+  int world;
+  long long n;
+  float* cur;
+  float* old;
+  const float* wgt;
+  int refresh_old;
+};
+
+__global__ void scalars_pull_kernel(ScalarArgs a) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long g = a.ids[i];
+    const float* src = a.shards[(int)(g % a.world)] + g / a.world;
+    float x;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(x) : "l"(src));
+    a.cur[i] = x;
+    if (a.old) a.old[i] = x;
+  }
+}
+
+__global__ void scalars_push_kernel(ScalarArgs a) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long g = a.ids[i];
+    float* dstp = a.shards[(int)(g % a.world)] + g / a.world;
+    float x = a.cur[i];
+    float d = a.old ? x - a.old[i] : x;
+    if (a.old && a.refresh_old) a.old[i] = x;
+    if (a.wgt) d *= a.wgt[i];
+    if (d != 0.f)
+      asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(dstp), "f"(d) : "memory");
+  }
+}
+
+// int32 rows (LDA word-topic counts): pull = copy, push = integer add of deltas.
+struct IRowArgs {
+  const long long* ids;
+  int* const* shards;
+  int world;
+  int D;  // ints per row, multiple of 4
+  long long n;
+  int* cur;
+  int* old;
+  int refresh_old;
+};
+
+__global__ void __launch_bounds__(256) irows_pull_kernel(IRowArgs a) {
+  const int vec_per_row = a.D >> 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (long long row = (long long)blockIdx.x * wpb + warp; row < a.n;
+       row += (long long)gridDim.x * wpb) {
+    long long g = a.ids[row];
+    const int* src = a.shards[(int)(g % a.world)] + (g / a.world) * a.D;
+    for (int v = lane; v < vec_per_row; v += 32) {
+      int4 x;
+      asm volatile("ld.relaxed.sys.global.v4.s32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w)
+                   : "l"(src + 4 * v));
+      *reinterpret_cast<int4*>(a.cur + row * a.D + 4 * v) = x;
+      if (a.old) *reinterpret_cast<int4*>(a.old + row * a.D + 4 * v) = x;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) irows_push_kernel(IRowArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (long long row = (long long)blockIdx.x * wpb + warp; row < a.n;
+       row += (long long)gridDim.x * wpb) {
+    long long g = a.ids[row];
+    int* dstp = a.shards[(int)(g % a.world)] + (g / a.world) * a.D;
+    for (int e = lane; e < a.D; e += 32) {
+      int x = a.cur[row * a.D + e];
+      int d = a.old ? x - a.old[row * a.D + e] : x;
+      if (a.old && a.refresh_old) a.old[row * a.D + e] = x;
+      if (d != 0)
+        asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(dstp + e), "r"(d)
+                     : "memory");
+    }
+  }
+}
+
+inline int grid_for(long long work_items, int per_block, int max_blocks) {
+  long long b = (work_items + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  if (b > max_blocks) b = max_blocks;
+  return (int)b;
+}
+
+}  // namespace
+
+PCL_API int pcl_rows_pull_f32(const long long* ids, float* const* shards, int world, int D,
+                              long long n, float* dst, float* dst0, const long long* clocks,
+                              long long target, unsigned long long timeout_ns,
+                              PclStatus* status, int rank, cudaStream_t stream) {
+  if (D <= 0 || (D & 3)) return (int)cudaErrorInvalidValue;
+  if (n <= 0 && !(clocks && target > 0)) return 0;
+  PullArgs a{ids, shards, world, D, n, dst, dst0, clocks, target, timeout_ns, status, rank};
+  int vec = D >> 2, tpr = 32;
+  while (tpr > vec) tpr >>= 1;
+  int grid = grid_for(n, 256 / tpr, 148 * 16);
+  rows_pull_kernel<<<grid, 256, 0, stream>>>(a);
+  return pcl_last_error();
+}
+
+PCL_API int pcl_rows_push_f32(const long long* ids, float* const* shards, int world, int D,
+                              long long n, float* cur, float* old, const float* wgt,
+                              float scale, int handler, int refresh_old,
+                              cudaStream_t stream) {
+  if (D <= 0 || (D & 3)) return (int)cudaErrorInvalidValue;
+  if (n <= 0) return 0;
+  PushArgs a{ids, shards, world, D, n, cur, old, wgt, scale, handler, refresh_old};
+  int vec = D >> 2, tpr = 32;
+  while (tpr > vec) tpr >>= 1;
+  int grid = grid_for(n, 256 / tpr, 148 * 16);
+  rows_push_kernel<<<grid, 256, 0, stream>>>(a);
+  return pcl_last_error();
+}
+
+PCL_API int pcl_scalars_pull_f32(const long long* ids, float* const* shards, int world,
+                                 long long n, float* cur, float* old, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  ScalarArgs a{ids, shards, world, n, cur, old, nullptr, 0};
+  scalars_pull_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, stream>>>(a);
+  return pcl_last_error();
+}
+
+PCL_API int pcl_scalars_push_f32(const long long* ids, float* const* shards, int world,
+                                 long long n, float* cur, float* old, const float* wgt,
+                                 int refresh_old, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  ScalarArgs a{ids, shards, world, n, cur, old, wgt, refresh_old};
+  scalars_push_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, stream>>>(a);
+  return pcl_last_error();
+}
+
+PCL_API int pcl_rows_pull_i32(const long long* ids, int* const* shards, int world, int D,
+                              long long n, int* cur, int* old, cudaStream_t stream) {
+  if (D <= 0 || (D & 3)) return (int)cudaErrorInvalidValue;
+  if (n <= 0) return 0;
+  IRowArgs a{ids, shards, world, D, n, cur, old, 0};
+  irows_pull_kernel<<<grid_for(n, 8, 148 * 16), 256, 0, stream>>>(a);
+  return pcl_last_error();
+}
+
+PCL_API int pcl_rows_push_i32(const long long* ids, int* const* shards, int world, int D,
+                              long long n, int* cur, int* old, int refresh_old,
+                              cudaStream_t stream) {
+  if (D <= 0 || (D & 3)) return (int)cudaErrorInvalidValue;
+  if (n <= 0) return 0;
+  IRowArgs a{ids, shards, world, D, n, cur, old, refresh_old};
+  irows_push_kernel<<<grid_for(n, 8, 148 * 16), 256, 0, stream>>>(a);
+  return pcl_last_error();
+}

@@ -1,0 +1,402 @@
+"""Biased matrix factorisation by SGD on GPUs with the parameter-server shards
+in HBM (device path of the reference's ``matrix_factorization`` paralg class,
+alg/recommendation/matrix_factorization/mf.hpp:46-378).
+
+One training round keeps the reference's structure (mf.hpp:282-323):
+
+    read_mf_paras   -> RowTable.pull   (peer loads; SSP staleness wait fused in)
+    local SGD pass  -> pcl_mf_sgd_pass (user-major chunks, vector reductions)
+    update_mf_fac / update_mf_bias
+                    -> RowTable.push   (wgt * (new - old) reduced into the owner)
+    iter_commit     -> DeviceSspClock.commit
+
+``wgt`` is 1 / (number of ranks that hold the row), gathered through a counter
+table exactly like the reference's ``<id>_u_cnt`` / ``<id>_i_cnt`` keys
+(mf.hpp:150-197).  Ratings are placed on a ``npx x npy`` rank grid by
+(user group, item group) (the reference's ``fsmap`` pattern,
+include/load/scheduler.hpp:81-92); groups can be balanced by rating mass so
+that heavy-tailed id distributions do not overload one rank.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..parallel.ssp_device import DeviceSspClock
+from ..ps.tables import RowTable, ScalarTable
+from ..utils.decomp import npfact2d
+
+
+def _pad_rank(k: int) -> int:
+    for d in (32, 64, 128, 256):
+        if k <= d:
+            return d
+    raise ValueError("factor rank above 256 is not supported by the SGD kernel")
+
+
+def balanced_groups(counts: torch.Tensor, ngroups: int) -> torch.Tensor:
+    """Assign ids to ``ngroups`` groups with near-equal total count.
+
+    The ``heavy`` ids (count above 1/(64*ngroups) of the total) are placed
+    greedily, largest first, on the lightest group; the light tail is dealt
+    round-robin, which is balanced in expectation.  Returns an int32 group id
+    per id.  With ``ngroups == 1`` everything is group 0.
+    """
+    n = counts.numel()
+    grp = (torch.arange(n, device=counts.device, dtype=torch.int64) % ngroups).to(torch.int32)
+    if ngroups == 1:
+        return grp
+    total = float(counts.sum().item())
+    thresh = total / (64.0 * ngroups)
+    heavy = torch.nonzero(counts.to(torch.float64) > thresh).flatten()
+    if heavy.numel() == 0:
+        return grp
+    hc = counts[heavy].to(torch.float64)
+    order = torch.argsort(hc, descending=True)
+    heavy, hc = heavy[order].cpu(), hc[order].cpu()
+    light_mask = torch.ones(n, dtype=torch.bool, device=counts.device)
+    light_mask[heavy.to(counts.device)] = False
+    load = torch.zeros(ngroups, dtype=torch.float64)
+    # tail contribution per group (round robin over ids)
+    tail = torch.zeros(ngroups, dtype=torch.float64, device=counts.device)
+    tail.index_add_(0, grp[light_mask].to(torch.int64), counts[light_mask].to(torch.float64))
+    load += tail.cpu()
+    g_heavy = torch.empty(heavy.numel(), dtype=torch.int32)
+    for j in range(heavy.numel()):
+        g = int(torch.argmin(load))
+        g_heavy[j] = g
+        load[g] += hc[j]
+    grp[heavy.to(counts.device)] = g_heavy.to(counts.device)
+    return grp
+
+
+class MfSgdGpu:
+    def __init__(self, n_users: int, n_items: int, k: int = 128, alpha: float = 0.005,
+                 beta: float = 0.02, rounds: int = 1, staleness: int = 2, ssp: bool = True,
+                 group=None, device=None, seed: int = 0, hot_mix: float = 1.0,
+                 sgd_blocks: int = 0, timeout_s: float = 5.0):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device if device is not None else
+                                   f"cuda:{torch.cuda.current_device()}")
+        self.n_users, self.n_items, self.k = int(n_users), int(n_items), int(k)
+        self.D = _pad_rank(self.k)
+        self.alpha, self.beta = float(alpha), float(beta)
+        self.rounds = int(rounds)
+        self.staleness = int(staleness) if ssp else 0
+        self.ssp = bool(ssp)
+        self.seed = seed
+        self.hot_mix = float(hot_mix)
+        self.sgd_blocks = int(sgd_blocks) if sgd_blocks > 0 else 148 * 4
+        self.npx, self.npy = npfact2d(self.world)
+        self.px, self.py = self.rank // self.npy, self.rank % self.npy
+        # parameter-server tables (shards in HBM)
+        self.Wt = RowTable(self.n_users, self.D, torch.float32, group, self.device)
+        self.Ht = RowTable(self.n_items, self.D, torch.float32, group, self.device)
+        self.but = ScalarTable(self.n_users, group, self.device)
+        self.bit = ScalarTable(self.n_items, group, self.device)
+        self.clock = DeviceSspClock(self.staleness, self.rounds, group, self.device, timeout_s)
+        self.mu = 0.0
+        self.nnz = 0
+        self.sse = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self.host_stream = None
+        self.h2d_bytes = 0
+        self._loaded = False
+
+    # ------------------------------------------------------------------ data
+    def owner_of(self, ugrp: torch.Tensor, igrp: torch.Tensor) -> torch.Tensor:
+        return ugrp.to(torch.int64) * self.npy + igrp.to(torch.int64)
+
+    def load_ratings(self, u: torch.Tensor, i: torch.Tensor, r: torch.Tensor,
+                     keep_on_host: bool = False):
+        """Take this rank's ratings (global ids) and build the device layout.
+
+        The ratings are sorted user-major, padded to whole chunks of 32 and the
+        chunks are shuffled once, so that the chunks of one heavy user are
+        spread over the pass and ratings are still read sequentially.  With
+        ``keep_on_host`` the chunked arrays are kept in pinned host memory and
+        streamed to the GPU every round (out-of-core mode).
+        """
+        dev = self.device
+        u = u.to(dev, torch.int64)
+        i = i.to(dev, torch.int64)
+        r = r.to(dev, torch.float32)
+        nnz = u.numel()
+        self.nnz = nnz
+        self.lu, ru = torch.unique(u, return_inverse=True)
+        self.li, ri = torch.unique(i, return_inverse=True)
+        cu = torch.bincount(ru, minlength=self.lu.numel())
+        ci = torch.bincount(ri, minlength=self.li.numel())
+        order = torch.argsort(ru, stable=True)
+        ru, ri, r = ru[order].to(torch.int32), ri[order].to(torch.int32), r[order]
+        del order
+        pad = (-nnz) % 32
+        if pad:
+            ru = torch.cat([ru, torch.full((pad,), -1, dtype=torch.int32, device=dev)])
+            ri = torch.cat([ri, torch.zeros(pad, dtype=torch.int32, device=dev)])
+            r = torch.cat([r, torch.zeros(pad, dtype=torch.float32, device=dev)])
+        nch = ru.numel() // 32
+        g = torch.Generator(device=dev)
+        g.manual_seed(self.seed * 7919 + 17 + self.rank)
+        perm = torch.randperm(nch, device=dev, generator=g)
+        ru = ru.view(nch, 32)[perm].contiguous().view(-1)
+        ri = ri.view(nch, 32)[perm].contiguous().view(-1)
+        r = r.view(nch, 32)[perm].contiguous().view(-1)
+        del perm
+        self.nchunks = nch
+        # concurrency weights (see csrc/cuda/mf.cu): expected number of resident
+        # warps that touch the same row at the same time
+        P = min(self.sgd_blocks * 8, max(nch, 1))
+        denom = max(nnz, 1)
+        self.su = (1.0 / torch.clamp(self.hot_mix * P * cu.to(torch.float32) / denom, min=1.0)).contiguous()
+        self.si = (1.0 / torch.clamp(self.hot_mix * P * ci.to(torch.float32) / denom, min=1.0)).contiguous()
+        nU, nI = self.lu.numel(), self.li.numel()
+        self.Wl = torch.empty(nU, self.D, device=dev)
+        self.W0 = torch.empty(nU, self.D, device=dev)
+        self.Hl = torch.empty(nI, self.D, device=dev)
+        self.H0 = torch.empty(nI, self.D, device=dev)
+        self.bul = torch.empty(nU, device=dev)
+        self.bu0 = torch.empty(nU, device=dev)
+        self.bil = torch.empty(nI, device=dev)
+        self.bi0 = torch.empty(nI, device=dev)
+        if keep_on_host:
+            self.h_ru = ru.cpu().pin_memory()
+            self.h_ri = ri.cpu().pin_memory()
+            self.h_rr = r.cpu().pin_memory()
+            self.ru = self.ri = self.rr = None
+        else:
+            self.ru, self.ri, self.rr = ru, ri, r
+            self.h_ru = None
+        self._sum_r = float(r.sum(dtype=torch.float64).item())
+        self._loaded = True
+
+    def offload_ratings(self):
+        """Switch to out-of-core mode: move the chunked ratings to pinned host memory."""
+        if self.h_ru is not None:
+            return
+        torch.cuda.synchronize(self.device)
+        self.h_ru = self.ru.cpu().pin_memory()
+        self.h_ri = self.ri.cpu().pin_memory()
+        self.h_rr = self.rr.cpu().pin_memory()
+        self.ru = self.ri = self.rr = None
+
+    # ------------------------------------------------------------ parameters
+    def init_parameters(self):
+        """Owner-side initialisation: factors U(0, 0.1), biases 0.1*U(0,1), mu = global
+        mean rating (mf.hpp:127-143), then the holder counts -> push weights."""
+        assert self._loaded
+        dev = self.device
+        g = torch.Generator(device=dev)
+        g.manual_seed(self.seed * 1000003 + self.rank)
+        for t, rows in ((self.Wt, self.n_users), (self.Ht, self.n_items)):
+            t.shard.zero_()
+            t.shard[:, : self.k] = 0.1 * torch.rand(t.rows_per_shard, self.k, device=dev, generator=g)
+        self.but.shard.copy_(0.1 * torch.rand(self.but.rows_per_shard, device=dev, generator=g))
+        self.bit.shard.copy_(0.1 * torch.rand(self.bit.rows_per_shard, device=dev, generator=g))
+        tot = torch.tensor([self._sum_r, float(self.nnz)], dtype=torch.float64, device=dev)
+        if self.world > 1:
+            dist.all_reduce(tot, group=self.group)
+        self.mu = float(tot[0].item() / max(tot[1].item(), 1.0))
+        self.total_nnz = int(tot[1].item())
+        # holder counts through counter tables
+        cu = ScalarTable(self.n_users, self.group, dev)
+        ci = ScalarTable(self.n_items, self.group, dev)
+        ones_u = torch.ones(self.lu.numel(), device=dev)
+        ones_i = torch.ones(self.li.numel(), device=dev)
+        cu.push(self.lu, ones_u)
+        ci.push(self.li, ones_i)
+        self._barrier()
+        cnt_u = torch.empty_like(ones_u)
+        cnt_i = torch.empty_like(ones_i)
+        cu.pull(self.lu, cnt_u)
+        ci.pull(self.li, cnt_i)
+        self.wgt_u = (1.0 / cnt_u.clamp(min=1.0)).contiguous()
+        self.wgt_i = (1.0 / cnt_i.clamp(min=1.0)).contiguous()
+        self._barrier()
+        cu.free()
+        ci.free()
+        self._have_cache = False
+
+    def _barrier(self):
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    # ----------------------------------------------------------------- round
+    def pull(self, fused_wait: bool = True):
+        target = self.clock.wait_target() if (self.world > 1 and fused_wait) else 0
+        self.Wt.pull(self.lu, self.Wl, self.W0, self.clock.clocks, target,
+                     self.clock.timeout_ns, self.clock.status)
+        self.Ht.pull(self.li, self.Hl, self.H0)
+        self.but.pull(self.lu, self.bul, self.bu0)
+        self.bit.pull(self.li, self.bil, self.bi0)
+        self._have_cache = True
+
+    def sgd_pass(self):
+        s = _lib.stream_ptr()
+        if self.h_ru is None:
+            _lib.call("pcl_mf_sgd_pass", self.ru, self.ri, self.rr, self.ru.numel(), self.Wl,
+                      self.Hl, self.bul, self.bil, self.su, self.si, self.D, self.mu,
+                      self.alpha, self.beta, 1, self.sgd_blocks, self.sse, s)
+        else:
+            self._sgd_pass_streamed()
+
+    def _sgd_pass_streamed(self, nseg: int = 16):
+        """Out-of-core pass: ratings come from pinned host memory in segments; the copy
+        of segment s+1 overlaps the SGD kernel of segment s (two staging buffers)."""
+        dev = self.device
+        n = self.h_ru.numel()
+        seg = ((n // 32 + nseg - 1) // nseg) * 32
+        if self.host_stream is None:
+            self.host_stream = torch.cuda.Stream(device=dev)
+            self._stage = [(torch.empty(seg, dtype=torch.int32, device=dev),
+                            torch.empty(seg, dtype=torch.int32, device=dev),
+                            torch.empty(seg, dtype=torch.float32, device=dev)) for _ in range(2)]
+            self._copied = [torch.cuda.Event() for _ in range(2)]
+            self._consumed = [torch.cuda.Event() for _ in range(2)]
+        main = torch.cuda.current_stream(dev)
+        self.h2d_bytes = 0
+        k = 0
+        for off in range(0, n, seg):
+            m = min(seg, n - off)
+            b = k % 2
+            bru, bri, brr = self._stage[b]
+            with torch.cuda.stream(self.host_stream):
+                if k >= 2:
+                    self.host_stream.wait_event(self._consumed[b])
+                bru[:m].copy_(self.h_ru[off:off + m], non_blocking=True)
+                bri[:m].copy_(self.h_ri[off:off + m], non_blocking=True)
+                brr[:m].copy_(self.h_rr[off:off + m], non_blocking=True)
+                self._copied[b].record(self.host_stream)
+            self.h2d_bytes += 12 * m
+            main.wait_event(self._copied[b])
+            _lib.call("pcl_mf_sgd_pass", bru, bri, brr, m, self.Wl, self.Hl, self.bul, self.bil,
+                      self.su, self.si, self.D, self.mu, self.alpha, self.beta, 1,
+                      self.sgd_blocks, self.sse, main.cuda_stream)
+            self._consumed[b].record(main)
+            k += 1
+
+    def push(self):
+        self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u)
+        self.Ht.push(self.li, self.Hl, self.H0, self.wgt_i)
+        self.but.push(self.lu, self.bul, self.bu0, self.wgt_u)
+        self.bit.push(self.li, self.bil, self.bi0, self.wgt_i)
+
+    def need_pull(self) -> bool:
+        """SSP cache rule (include/ps.hpp:437-457): first and last read always pull; with
+        staleness s a cached copy may be reused while it is less than s clocks old."""
+        c = self.clock.clock
+        if not self._have_cache or not self.ssp or self.staleness == 0:
+            return True
+        if c == 0 or c >= self.rounds:
+            return True
+        return (c - self._pulled_at) >= self.staleness
+
+    def round(self):
+        if self.need_pull():
+            self.pull()
+            self._pulled_at = self.clock.clock
+        elif self.world > 1:
+            self.clock.wait()  # keep the staleness bound while serving from the cache
+        self.sse.zero_()
+        self.sgd_pass()
+        self.push()
+        if not self.ssp and self.world > 1:
+            self._barrier()
+        self.clock.commit()
+
+    def fit(self):
+        for _ in range(self.rounds):
+            self.round()
+        self._barrier()
+        self.clock.check()
+        self.pull(fused_wait=False)
+        self._barrier()
+
+    # --------------------------------------------------------------- metrics
+    def running_rmse(self) -> float:
+        """RMSE of the pre-update errors seen by the last SGD pass (8-byte D2H read)."""
+        tot = self.sse.clone()
+        if self.world > 1:
+            dist.all_reduce(tot, group=self.group)
+        return math.sqrt(float(tot.item()) / max(self.total_nnz, 1))
+
+    def rmse(self) -> float:
+        """Training RMSE of the clipped estimate with the current working copies
+        (cal_rmse, mf.hpp:94-108)."""
+        out = torch.zeros(1, dtype=torch.float64, device=self.device)
+        ru, ri, rr = self._device_ratings()
+        _lib.call("pcl_mf_sse", ru, ri, rr, ru.numel(), self.Wl, self.Hl, self.bul, self.bil,
+                  self.D, self.mu, out, None, _lib.stream_ptr())
+        # padding entries have u < 0 and predict mu against rating 0: remove them
+        pad = ru.numel() - self.nnz
+        out -= pad * (self.mu ** 2)
+        if self.world > 1:
+            dist.all_reduce(out, group=self.group)
+        return math.sqrt(max(float(out.item()), 0.0) / max(self.total_nnz, 1))
+
+    def _device_ratings(self):
+        if self.h_ru is None:
+            return self.ru, self.ri, self.rr
+        dev = self.device
+        return self.h_ru.to(dev), self.h_ri.to(dev), self.h_rr.to(dev)
+
+    def predict(self, u: torch.Tensor, i: torch.Tensor) -> torch.Tensor:
+        """Clipped estimate for (user, item) pairs by global id; unseen ids predict mu."""
+        dev = self.device
+        u = u.to(dev, torch.int64)
+        i = i.to(dev, torch.int64)
+        pu = torch.searchsorted(self.lu, u).clamp(max=max(self.lu.numel() - 1, 0))
+        pi = torch.searchsorted(self.li, i).clamp(max=max(self.li.numel() - 1, 0))
+        ok = (self.lu[pu] == u) & (self.li[pi] == i)
+        pu = torch.where(ok, pu, torch.full_like(pu, -1)).to(torch.int32).contiguous()
+        pi = torch.where(ok, pi, torch.full_like(pi, -1)).to(torch.int32).contiguous()
+        pred = torch.empty(u.numel(), device=dev)
+        _lib.call("pcl_mf_sse", pu, pi, None, u.numel(), self.Wl, self.Hl, self.bul, self.bil,
+                  self.D, self.mu, None, pred, _lib.stream_ptr())
+        return pred
+
+    # ------------------------------------------------------------------ dump
+    def dump_result(self, outdir: str):
+        """Write miu_0, ubias_0, ibias_0, W_0, H_0 in the reference's text layout
+        (mf.hpp:380-492): rank 0 writes what each owner holds, shard by shard."""
+        from ..utils.dump import dump_dict_scalar, dump_dict_vector
+        os.makedirs(outdir, exist_ok=True)
+        self._barrier()
+        parts = {}
+        for name, t, width in (("W_", self.Wt, self.k), ("H_", self.Ht, self.k)):
+            ids = t.owned_ids().cpu()
+            vals = t.shard[: ids.numel(), :width].cpu()
+            parts[name] = (ids, vals)
+        for name, t in (("ubias_", self.but), ("ibias_", self.bit)):
+            ids = t.owned_ids().cpu()
+            parts[name] = (ids, t.shard[: ids.numel()].cpu())
+        gathered = [parts]
+        if self.world > 1:
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, parts, group=self.group)
+        if self.rank == 0:
+            dump_dict_scalar({"miu": self.mu, "rating_sz": float(self.total_nnz)},
+                             os.path.join(outdir, "miu_0"))
+            for name in ("ubias_", "ibias_"):
+                with open(os.path.join(outdir, name + "0"), "w") as f:
+                    for p in gathered:
+                        ids, vals = p[name]
+                        dump_dict_scalar(dict(zip(ids.tolist(), vals.tolist())), f)
+            for name in ("W_", "H_"):
+                with open(os.path.join(outdir, name + "0"), "w") as f:
+                    for p in gathered:
+                        ids, vals = p[name]
+                        dump_dict_vector(dict(zip(ids.tolist(), vals.tolist())), f)
+        self._barrier()
+
+    def free(self):
+        self._barrier()
+        for t in (self.Wt, self.Ht, self.but, self.bit, self.clock):
+            t.free()

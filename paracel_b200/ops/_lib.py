@@ -1,0 +1,139 @@
+"""ctypes access to ``libpcl_kernels.so`` (the hand-written sm_100a kernels).
+
+Every exported launcher has a C ABI, takes raw device pointers plus a CUDA
+stream, and returns a ``cudaError_t``.  The table below is the single place
+where the argument types are declared; ``call(name, *args)`` converts tensors
+to their data pointers, checks the return code, and raises on failure.
+
+If a CUDA device is present but the library has not been built the import of
+any op fails loudly: there is no silent PyTorch fallback for these ops.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libpcl_kernels.so"
+
+_T = {
+    "p": ctypes.c_void_p,
+    "i": ctypes.c_int,
+    "q": ctypes.c_longlong,
+    "Q": ctypes.c_ulonglong,
+    "f": ctypes.c_float,
+    "d": ctypes.c_double,
+    "z": ctypes.c_size_t,
+}
+
+# name -> argument spec (stream is the trailing "p" where present)
+SIGS = {
+    "pcl_symm_alloc": "zpp",
+    "pcl_symm_open": "pp",
+    "pcl_symm_close": "p",
+    "pcl_symm_free": "p",
+    "pcl_device_sync": "",
+    "pcl_rows_pull_f32": "ppiiqpppqQpip",
+    "pcl_rows_push_f32": "ppiiqpppfiip",
+    "pcl_scalars_pull_f32": "ppiqppp",
+    "pcl_scalars_push_f32": "ppiqpppip",
+    "pcl_rows_pull_i32": "ppiiqppp",
+    "pcl_rows_push_i32": "ppiiqppip",
+    "pcl_mf_sgd_pass": "pppqppppppifffqipp",
+    "pcl_mf_sse": "pppqppppifppp",
+    "pcl_ssp_commit": "piiqp",
+    "pcl_ssp_wait": "piqQpip",
+}
+
+
+class KernelLibraryMissing(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def register(name: str, spec: str) -> None:
+    """Declare the signature of one more exported launcher."""
+    SIGS[name] = spec
+    if _LIB is not None:
+        _bind(name, spec)
+
+
+def _bind(name, spec):
+    fn = getattr(_LIB, name)
+    fn.argtypes = [_T[c] for c in spec]
+    fn.restype = ctypes.c_int
+    return fn
+
+
+def load():
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not _LIB_PATH.exists():
+        if os.environ.get("PCL_NO_AUTOBUILD", "0") != "1":
+            try:
+                from .. import _build
+                _build.build_kernels()
+            except Exception as e:  # pragma: no cover - build environment specific
+                raise KernelLibraryMissing(
+                    f"{_LIB_PATH} is missing and could not be built: {e}") from e
+        if not _LIB_PATH.exists():
+            raise KernelLibraryMissing(f"{_LIB_PATH} is missing; run python -m paracel_b200._build")
+    _LIB = ctypes.CDLL(str(_LIB_PATH))
+    for name, spec in SIGS.items():
+        if hasattr(_LIB, name):
+            _bind(name, spec)
+    _LIB.pcl_error_string.restype = ctypes.c_char_p
+    _LIB.pcl_error_string.argtypes = [ctypes.c_int]
+    return _LIB
+
+
+def available() -> bool:
+    return torch.cuda.is_available() and _LIB_PATH.exists()
+
+
+def _conv(a):
+    if a is None:
+        return None
+    if isinstance(a, torch.Tensor):
+        return a.data_ptr()
+    return a
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_LAUNCHES = 0
+
+
+def launches() -> int:
+    """Number of kernel-launching calls made through :func:`call` so far."""
+    return _LAUNCHES
+
+
+def call(name: str, *args) -> None:
+    global _LAUNCHES
+    lib = load()
+    fn = getattr(lib, name)
+    rc = fn(*[_conv(a) for a in args])
+    _LAUNCHES += 1
+    if rc != 0:
+        msg = lib.pcl_error_string(rc).decode()
+        raise RuntimeError(f"{name} failed: CUDA error {rc} ({msg})")
+
+
+def check_cuda(t: torch.Tensor, dtype, name: str):
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t

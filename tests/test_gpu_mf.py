@@ -1,0 +1,203 @@
+"""GPU tests of the sparse row pull/push kernels, the device SSP clock and the
+MF-SGD pass, each against a plain PyTorch / Python fp64 oracle."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _seq_mf_pass(u, i, r, W, H, bu, bi, mu, alpha, beta):
+    """Sequential fp64 pass in the given order (mf.hpp:266-280)."""
+    W, H, bu, bi = W.double().clone(), H.double().clone(), bu.double().clone(), bi.double().clone()
+    for uu, ii, rr in zip(u.tolist(), i.tolist(), r.tolist()):
+        pred = mu + bu[uu] + bi[ii] + (W[uu] * H[ii]).sum()
+        pred = min(5.0, max(1.0, float(pred)))
+        e = rr - pred
+        dW = alpha * (2 * e * H[ii] - beta * W[uu])
+        dH = alpha * (2 * e * W[uu] - beta * H[ii])
+        W[uu] += dW
+        H[ii] += dH
+        bu[uu] += alpha * (2 * e - beta * bu[uu])
+        bi[ii] += alpha * (2 * e - beta * bi[ii])
+    return W, H, bu, bi
+
+
+def test_rows_pull_push_match_index_ops():
+    from paracel_b200.ps.tables import RowTable, ScalarTable
+    dev = "cuda:0"
+    torch.manual_seed(0)
+    for width in (4, 8, 128, 132):
+        t = RowTable(1000, width, torch.float32, device=dev)
+        t.shard.copy_(torch.randn_like(t.shard))
+        ref = t.shard.clone()
+        ids = torch.randint(0, 1000, (777,), device=dev)
+        ids = torch.unique(ids)
+        cur = torch.empty(ids.numel(), width, device=dev)
+        old = torch.empty_like(cur)
+        t.pull(ids, cur, old)
+        torch.cuda.synchronize()
+        assert torch.equal(cur, ref[ids]) and torch.equal(old, ref[ids])
+        delta = torch.randn_like(cur)
+        cur += delta
+        wgt = torch.rand(ids.numel(), device=dev)
+        t.push(ids, cur, old, wgt)
+        torch.cuda.synchronize()
+        exp = ref.clone()
+        exp[ids] += wgt[:, None] * delta
+        torch.testing.assert_close(t.shard, exp, rtol=1e-5, atol=1e-5)
+        assert torch.equal(old, cur)  # snapshot refreshed
+        # duplicate ids accumulate
+        dup = torch.tensor([3, 3, 3, 5], device=dev)
+        ones = torch.ones(4, width, device=dev)
+        before = t.shard.clone()
+        t.push(dup, ones)
+        torch.cuda.synchronize()
+        assert torch.allclose(t.shard[3], before[3] + 3) and torch.allclose(t.shard[5], before[5] + 1)
+        # max handler
+        big = torch.full((1, width), 1e6, device=dev)
+        t.push(torch.tensor([7], device=dev), big, handler="max")
+        neg = torch.full((1, width), -1e6, device=dev)
+        t.push(torch.tensor([8], device=dev), neg, handler="max")
+        torch.cuda.synchronize()
+        assert torch.all(t.shard[7] == 1e6)
+        assert torch.equal(t.shard[8], before[8])
+        t.free()
+    s = ScalarTable(500, device=dev)
+    ids = torch.arange(0, 500, 3, device=dev)
+    v = torch.randn(ids.numel(), device=dev)
+    s.push(ids, v)
+    out = torch.empty_like(v)
+    s.pull(ids, out)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out, v)
+    s.free()
+
+
+def test_rows_int32():
+    from paracel_b200.ps.tables import RowTable
+    dev = "cuda:0"
+    t = RowTable(300, 1024, torch.int32, device=dev)
+    ids = torch.tensor([1, 5, 299], device=dev)
+    cur = torch.zeros(3, 1024, dtype=torch.int32, device=dev)
+    old = torch.zeros_like(cur)
+    t.pull(ids, cur, old)
+    cur += torch.arange(1024, device=dev, dtype=torch.int32)[None, :] - 512
+    t.push(ids, cur, old)
+    t.push(ids, cur - old + torch.ones_like(cur))  # old == cur after refresh -> adds ones
+    torch.cuda.synchronize()
+    exp = torch.arange(1024, device=dev, dtype=torch.int32) - 512 + 1
+    assert torch.equal(t.shard[5], exp) and torch.equal(t.shard[299], exp)
+    assert int(t.shard[2].abs().sum()) == 0
+    t.free()
+
+
+def test_ssp_clock_commit_wait_and_timeout():
+    from paracel_b200.parallel.ssp_device import DeviceSspClock, SspTimeout, DEPARTED
+    c = DeviceSspClock(staleness=1, total_iters=3, device="cuda:0", timeout_s=0.05)
+    c.wait()
+    c.check()
+    c.commit()
+    c.commit()
+    torch.cuda.synchronize()
+    assert int(c.clocks[0]) == 2
+    c.wait()
+    c.check()
+    # a flag that nothing sets: the wait must give up and report, not hang
+    c.clock = 10
+    c.wait()
+    with pytest.raises(SspTimeout) as ei:
+        c.check()
+    assert ei.value.expected == 9 and ei.value.seen == 2
+    c.clock = 2
+    c.commit()  # reaches total_iters: departs
+    torch.cuda.synchronize()
+    assert int(c.clocks[0]) == DEPARTED
+    c.free()
+
+
+def test_mf_single_chunk_matches_sequential_oracle():
+    from paracel_b200.models.mf_gpu import MfSgdGpu
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(3)
+    for k in (32, 80, 128):
+        nu, ni, nnz = 6, 9, 31
+        u = torch.randint(0, nu, (nnz,), generator=g)
+        i = torch.randint(0, ni, (nnz,), generator=g)
+        r = torch.randint(1, 6, (nnz,), generator=g).float()
+        m = MfSgdGpu(nu, ni, k=k, alpha=0.05, beta=0.02, rounds=1, device=dev)
+        m.load_ratings(u, i, r)
+        m.init_parameters()
+        assert torch.all(m.su == 1) and torch.all(m.si == 1)
+        W0 = m.Wt.shard[:nu, :k].cpu()
+        H0 = m.Ht.shard[:ni, :k].cpu()
+        bu0, bi0 = m.but.shard[:nu].cpu(), m.bit.shard[:ni].cpu()
+        order = torch.argsort(u, stable=True)
+        We, He, bue, bie = _seq_mf_pass(u[order], i[order], r[order], W0, H0, bu0, bi0, m.mu,
+                                        0.05, 0.02)
+        m.round()
+        torch.cuda.synchronize()
+        lu, li = m.lu.cpu(), m.li.cpu()
+        torch.testing.assert_close(m.Wt.shard[:nu, :k].cpu()[lu].double(), We[lu], rtol=2e-4, atol=2e-5)
+        torch.testing.assert_close(m.Ht.shard[:ni, :k].cpu()[li].double(), He[li], rtol=2e-4, atol=2e-5)
+        torch.testing.assert_close(m.but.shard[:nu].cpu()[lu].double(), bue[lu], rtol=2e-4, atol=2e-5)
+        torch.testing.assert_close(m.bit.shard[:ni].cpu()[li].double(), bie[li], rtol=2e-4, atol=2e-5)
+        if k < m.D:
+            assert float(m.Wt.shard[:, k:].abs().sum()) == 0.0
+        m.free()
+
+
+def test_mf_converges_like_sequential_pass():
+    from paracel_b200.models.mf_gpu import MfSgdGpu
+    from paracel_b200.utils.synth import MfRatingStream
+    dev = "cuda:0"
+    nu, ni, nnz, k = 2000, 600, 30_000, 32
+    st = MfRatingStream(nu, ni, nnz, seed=5, device=dev)
+    u, i, r = st.chunk_at(0)
+    rounds = 4
+    m = MfSgdGpu(nu, ni, k=k, alpha=0.005, beta=0.02, rounds=rounds, device=dev, staleness=0,
+                 ssp=False)
+    m.load_ratings(u, i, r)
+    m.init_parameters()
+    m.pull()
+    r0 = m.rmse()
+    W0 = m.Wt.shard[:nu, :k].cpu()
+    H0 = m.Ht.shard[:ni, :k].cpu()
+    bu0, bi0 = m.but.shard[:nu].cpu(), m.bit.shard[:ni].cpu()
+    m.fit()
+    r_gpu = m.rmse()
+    # vectorised fp64 oracle: sequential pass in user-major order
+    order = torch.argsort(u.cpu(), stable=True)
+    uu, ii, rr = u.cpu()[order], i.cpu()[order], r.cpu()[order]
+    W, H, bu, bi = W0, H0, bu0, bi0
+    for _ in range(rounds):
+        W, H, bu, bi = _seq_mf_pass(uu[:], ii[:], rr[:], W, H, bu, bi, m.mu, 0.005, 0.02)
+    pred = (m.mu + bu[uu] + bi[ii] + (W[uu] * H[ii]).sum(1)).clamp(1, 5)
+    r_cpu = math.sqrt(float(((rr.double() - pred) ** 2).mean()))
+    pr = m.predict(u[:100], i[:100]).cpu()
+    assert torch.all((pr >= 1) & (pr <= 5))
+    m.free()
+    assert r_gpu < r0
+    assert abs(r_gpu - r_cpu) < 0.05 * r_cpu, (r0, r_gpu, r_cpu)
+
+
+def test_mf_streamed_rounds_equal_resident_rounds_statistically():
+    from paracel_b200.models.mf_gpu import MfSgdGpu
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(11)
+    nu, ni, nnz = 500, 300, 60_000
+    u = torch.randint(0, nu, (nnz,), device=dev, generator=g)
+    i = torch.randint(0, ni, (nnz,), device=dev, generator=g)
+    r = torch.randint(1, 6, (nnz,), device=dev, generator=g).float()
+    out = []
+    for host in (False, True):
+        m = MfSgdGpu(nu, ni, k=64, rounds=4, device=dev, seed=1)
+        m.load_ratings(u, i, r, keep_on_host=host)
+        m.init_parameters()
+        m.fit()
+        out.append(m.rmse())
+        if host:
+            assert m.h2d_bytes == 12 * m.nchunks * 32
+        m.free()
+    assert abs(out[0] - out[1]) < 0.02 * out[0], out
