@@ -35,6 +35,9 @@ struct MfArgs {
   long long nchunks;
   long long stride;  // coprime with nchunks: spreads the chunks of one heavy user in time
   double* sse;       // optional: += sum of squared pre-update errors (running training loss)
+  int hot_T;         // local item indices < hot_T are replicated in shared memory
+  int cpw;           // chunks per warp between two flushes of the hot replicas
+  float flush_scale; // mixing weight of one CTA's hot-row delta (1 / #CTAs)
 };
 
 template <int VEC>
@@ -73,53 +76,109 @@ __device__ __forceinline__ void red_row(float* p, const Row<VEC>& d) {
   }
 }
 
+// Shared-memory replicas of the hottest item rows.  Local item indices are
+// ordered so that the T most frequent items of the rank come first; a CTA keeps
+// the current value `hv` and the value at the start of the period `hbase` of
+// each of them (layout [row][k][lane], bank-conflict free for a warp).  Every
+// `cpw` chunks per warp the CTA reduces flush_scale * (hv - hbase) into the
+// global row, reloads it, and goes on: the hot rows see shared-memory atomics
+// (parallel over all SMs) instead of thousands of same-address L2 atomics, at
+// the price of a bounded staleness between CTAs -- the same parameter-mixing
+// rule the reference applies between workers (mf.hpp:217-262).
 template <int VEC>
-__global__ void __launch_bounds__(256, 4) mf_sgd_kernel(MfArgs a) {
+__global__ void __launch_bounds__(512, 2) mf_sgd_kernel(MfArgs a) {
   constexpr int D = VEC * 32;
+  extern __shared__ float smem[];
+  const int T = a.hot_T;
+  float* hv = smem;                    // T x D
+  float* hbase = hv + (size_t)T * D;   // T x D
+  float* hb = hbase + (size_t)T * D;   // T
+  float* hbb = hb + T;                 // T
   const int lane = threadIdx.x & 31;
-  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int wic = threadIdx.x >> 5;
+  const int wpc = blockDim.x >> 5;
   const float ab = a.alpha * a.beta;
   float sse = 0.f;
 
-  for (long long c = warp; c < a.nchunks; c += nwarps) {
-    const long long ch = (c * a.stride) % a.nchunks;
-    const long long base = ch * 32;
-    const long long rem = a.nnz - base;
-    const int n = rem < 32 ? (int)rem : 32;
-    int my_u = -1, my_i = 0;
-    float my_r = 0.f;
-    if (lane < n) {
-      my_u = __ldg(a.ru + base + lane);
-      my_i = __ldg(a.ri + base + lane);
-      my_r = __ldg(a.rr + base + lane);
+  const long long step = (long long)gridDim.x * wpc;
+  // uniform iteration count for every warp of this CTA (barriers inside the loop)
+  const long long cta_chunks = a.nchunks > blockIdx.x
+      ? (a.nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const long long iters = (cta_chunks + wpc - 1) / wpc;
+
+  for (long long it = 0; it < iters; ++it) {
+    if (T > 0 && (it % a.cpw) == 0) {
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < T * D; idx += blockDim.x) {
+        const int row = idx / D, e = idx % D;          // e = global element in the row
+        const int sidx = row * D + (e % VEC) * 32 + (e / VEC);
+        float* gp = a.H + (size_t)row * D + e;
+        if (it > 0) {
+          const float d = hv[sidx] - hbase[sidx];
+          if (d != 0.f) atomicAdd(gp, d * a.flush_scale);
+        }
+        const float v = __ldcg(gp);
+        hv[sidx] = v;
+        hbase[sidx] = v;
+      }
+      for (int row = threadIdx.x; row < T; row += blockDim.x) {
+        if (it > 0) {
+          const float d = hb[row] - hbb[row];
+          if (d != 0.f) atomicAdd(a.bi + row, d * a.flush_scale);
+        }
+        const float v = __ldcg(a.bi + row);
+        hb[row] = v;
+        hbb[row] = v;
+      }
+      __syncthreads();
     }
+    const long long c = (long long)blockIdx.x + ((long long)wic + it * wpc) * gridDim.x;
+    if (c >= a.nchunks) continue;  // warp-uniform; barriers above are still reached
+    const long long base = c * 32;
+    const int my_u = __ldg(a.ru + base + lane);
+    const int my_i = __ldg(a.ri + base + lane);
+    const float my_r = __ldg(a.rr + base + lane);
     int cur_u = -1;
     Row<VEC> w, w0;
     float bu = 0.f, bu0 = 0.f, s_u = 1.f;
 #pragma unroll
     for (int k = 0; k < VEC; ++k) { w.v[k] = 0.f; w0.v[k] = 0.f; }
 
-    // software prefetch of the first item row
+    // software prefetch of the first item row (cold rows only)
     int i_nxt = __shfl_sync(0xffffffffu, my_i, 0);
-    Row<VEC> h_nxt = load_row_cg<VEC>(a.H + (long long)i_nxt * D + lane * VEC);
-    float bi_nxt = __ldcg(a.bi + i_nxt);
     float si_nxt = __ldg(a.si + i_nxt);
+    Row<VEC> h_nxt;
+    float bi_nxt = 0.f;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) h_nxt.v[k] = 0.f;
+    if (i_nxt >= T) {
+      h_nxt = load_row_cg<VEC>(a.H + (long long)i_nxt * D + lane * VEC);
+      bi_nxt = __ldcg(a.bi + i_nxt);
+    }
 
-    for (int j = 0; j < n; ++j) {
+#pragma unroll 1
+    for (int j = 0; j < 32; ++j) {
       const int u = __shfl_sync(0xffffffffu, my_u, j);
       const int i = i_nxt;
       const float r = __shfl_sync(0xffffffffu, my_r, j);
+      const bool hot = i < T;
       Row<VEC> h = h_nxt;
-      const float bi = bi_nxt;
+      float bi = bi_nxt;
       const float s_i = si_nxt;
-      if (j + 1 < n) {
+      if (j + 1 < 32) {
         i_nxt = __shfl_sync(0xffffffffu, my_i, j + 1);
-        h_nxt = load_row_cg<VEC>(a.H + (long long)i_nxt * D + lane * VEC);
-        bi_nxt = __ldcg(a.bi + i_nxt);
         si_nxt = __ldg(a.si + i_nxt);
+        if (i_nxt >= T) {
+          h_nxt = load_row_cg<VEC>(a.H + (long long)i_nxt * D + lane * VEC);
+          bi_nxt = __ldcg(a.bi + i_nxt);
+        }
       }
       if (u < 0) continue;  // padding entry (warp-uniform)
+      if (hot) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) h.v[k] = hv[i * D + k * 32 + lane];
+        bi = hb[i];
+      }
       if (u != cur_u) {
         if (cur_u >= 0) {
           Row<VEC> d;
@@ -151,9 +210,21 @@ __global__ void __launch_bounds__(256, 4) mf_sgd_kernel(MfArgs a) {
         dh.v[k] = s_i * (a2e * wk - ab * hk);
         w.v[k] = wk + (a2e * hk - ab * wk);
       }
-      red_row<VEC>(a.H + (long long)i * D + lane * VEC, dh);
+      const float dbi = s_i * (a2e - ab * bi);
       bu += a2e - ab * bu;
-      if (lane == 0) atomicAdd(a.bi + i, s_i * (a2e - ab * bi));
+      if (hot) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) atomicAdd(&hv[i * D + k * 32 + lane], dh.v[k]);
+        if (lane == 0) atomicAdd(&hb[i], dbi);
+      } else {
+        red_row<VEC>(a.H + (long long)i * D + lane * VEC, dh);
+        if (lane == 0) atomicAdd(a.bi + i, dbi);
+        if (j + 1 < 32 && i_nxt == i) {  // the prefetched copy predates this update
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) h_nxt.v[k] += dh.v[k];
+          bi_nxt += dbi;
+        }
+      }
     }
     if (cur_u >= 0) {
       Row<VEC> d;
@@ -161,6 +232,19 @@ __global__ void __launch_bounds__(256, 4) mf_sgd_kernel(MfArgs a) {
       for (int k = 0; k < VEC; ++k) d.v[k] = s_u * (w.v[k] - w0.v[k]);
       red_row<VEC>(a.W + (long long)cur_u * D + lane * VEC, d);
       if (lane == 0) atomicAdd(a.bu + cur_u, s_u * (bu - bu0));
+    }
+  }
+  if (T > 0) {  // final flush of the hot replicas
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < T * D; idx += blockDim.x) {
+      const int row = idx / D, e = idx % D;
+      const int sidx = row * D + (e % VEC) * 32 + (e / VEC);
+      const float d = hv[sidx] - hbase[sidx];
+      if (d != 0.f) atomicAdd(a.H + (size_t)row * D + e, d * a.flush_scale);
+    }
+    for (int row = threadIdx.x; row < T; row += blockDim.x) {
+      const float d = hb[row] - hbb[row];
+      if (d != 0.f) atomicAdd(a.bi + row, d * a.flush_scale);
     }
   }
   if (a.sse != nullptr && lane == 0 && sse != 0.f) atomicAdd(a.sse, (double)sse);
@@ -222,33 +306,58 @@ __global__ void __launch_bounds__(256) mf_rmse_kernel(RmseArgs a) {
 
 }  // namespace
 
-// One SGD pass over `nnz` user-major sorted ratings (entries with a negative
-// user index are padding and are skipped; `sse`, if given, accumulates the
-// squared pre-update errors).  D must be 32, 64, 128 or
+// One SGD pass over `nnz` user-major sorted ratings, nnz a multiple of 32
+// (entries with a negative user index are padding and are skipped; `sse`, if
+// given, accumulates the squared pre-update errors).  D must be 32, 64, 128 or
 // 256 (pad the factors with zeros otherwise: zero columns stay zero under the
-// update rule).  `blocks` <= 0 selects 148 SMs x 4 resident blocks.
+// update rule).  `blocks` <= 0 selects 2 CTAs of 512 threads per SM.  Local
+// item indices below `hot_T` are served from shared-memory replicas that are
+// mixed into the global rows every `cpw` chunks per warp with weight
+// `flush_scale` (<= 0: 1 / blocks).
 PCL_API int pcl_mf_sgd_pass(const int* ru, const int* ri, const float* rr, long long nnz,
                             float* W, float* H, float* bu, float* bi, const float* su,
                             const float* si, int D, float mu, float alpha, float beta,
-                            long long stride, int blocks, double* sse, cudaStream_t stream) {
+                            int hot_T, int cpw, float flush_scale, int blocks, double* sse,
+                            cudaStream_t stream) {
   if (nnz <= 0) return 0;
+  if (nnz % 32 != 0 || hot_T < 0) return (int)cudaErrorInvalidValue;
   MfArgs a;
   a.ru = ru; a.ri = ri; a.rr = rr; a.nnz = nnz;
   a.W = W; a.H = H; a.bu = bu; a.bi = bi; a.su = su; a.si = si;
   a.mu = mu; a.alpha = alpha; a.beta = beta;
-  a.nchunks = (nnz + 31) / 32;
-  a.stride = (stride > 0 && stride < a.nchunks) ? stride : 1;
+  a.nchunks = nnz / 32;
+  a.stride = 1;
   a.sse = sse;
-  if (blocks <= 0) blocks = 148 * 4;
-  long long need = (a.nchunks + 7) / 8;
+  a.hot_T = hot_T;
+  a.cpw = cpw > 0 ? cpw : 8;
+  const int threads = 512;
+  if (blocks <= 0) blocks = 148 * 2;
+  long long need = (a.nchunks + (threads / 32) - 1) / (threads / 32);
   if (need < blocks) blocks = (int)need;
+  a.flush_scale = flush_scale > 0.f ? flush_scale : 1.f / (float)blocks;
+  size_t smem = (size_t)hot_T * (2 * (size_t)D + 2) * sizeof(float);
+  if (smem > 110 * 1024) return (int)cudaErrorInvalidValue;
+  cudaError_t e = cudaSuccess;
   switch (D) {
-    case 32: mf_sgd_kernel<1><<<blocks, 256, 0, stream>>>(a); break;
-    case 64: mf_sgd_kernel<2><<<blocks, 256, 0, stream>>>(a); break;
-    case 128: mf_sgd_kernel<4><<<blocks, 256, 0, stream>>>(a); break;
-    case 256: mf_sgd_kernel<8><<<blocks, 256, 0, stream>>>(a); break;
+    case 32:
+      e = cudaFuncSetAttribute(mf_sgd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess) mf_sgd_kernel<1><<<blocks, threads, smem, stream>>>(a);
+      break;
+    case 64:
+      e = cudaFuncSetAttribute(mf_sgd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess) mf_sgd_kernel<2><<<blocks, threads, smem, stream>>>(a);
+      break;
+    case 128:
+      e = cudaFuncSetAttribute(mf_sgd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess) mf_sgd_kernel<4><<<blocks, threads, smem, stream>>>(a);
+      break;
+    case 256:
+      e = cudaFuncSetAttribute(mf_sgd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess) mf_sgd_kernel<8><<<blocks, threads, smem, stream>>>(a);
+      break;
     default: return (int)cudaErrorInvalidValue;
   }
+  if (e != cudaSuccess) return (int)e;
   return pcl_last_error();
 }
 

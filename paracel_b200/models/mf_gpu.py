@@ -79,7 +79,8 @@ class MfSgdGpu:
     def __init__(self, n_users: int, n_items: int, k: int = 128, alpha: float = 0.005,
                  beta: float = 0.02, rounds: int = 1, staleness: int = 2, ssp: bool = True,
                  group=None, device=None, seed: int = 0, hot_mix: float = 1.0,
-                 sgd_blocks: int = 0, timeout_s: float = 5.0):
+                 sgd_blocks: int = 0, timeout_s: float = 5.0, hot_rows: int = 106,
+                 chunks_per_flush: int = 8):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -93,7 +94,10 @@ class MfSgdGpu:
         self.ssp = bool(ssp)
         self.seed = seed
         self.hot_mix = float(hot_mix)
-        self.sgd_blocks = int(sgd_blocks) if sgd_blocks > 0 else 148 * 4
+        self.sgd_blocks = int(sgd_blocks) if sgd_blocks > 0 else 148 * 2
+        self.warps_per_block = 16
+        self.hot_rows = int(hot_rows)
+        self.chunks_per_flush = int(chunks_per_flush)
         self.npx, self.npy = npfact2d(self.world)
         self.px, self.py = self.rank // self.npy, self.rank % self.npy
         # parameter-server tables (shards in HBM)
@@ -133,6 +137,25 @@ class MfSgdGpu:
         self.li, ri = torch.unique(i, return_inverse=True)
         cu = torch.bincount(ru, minlength=self.lu.numel())
         ci = torch.bincount(ri, minlength=self.li.numel())
+        # resident warps = expected number of ratings in flight at any time
+        P = self.sgd_blocks * self.warps_per_block
+        # hot items: those that several resident warps would update at once; they
+        # take the first local indices and are replicated in shared memory
+        conc = P * ci.to(torch.float64) / max(nnz, 1)
+        T = int(min(self.hot_rows, int((conc > 1.0).sum().item()), self.li.numel()))
+        T = min(T, (110 * 1024) // ((2 * self.D + 2) * 4))
+        self.hot_T = T
+        if T > 0:
+            hot = torch.topk(ci, T).indices
+            mask = torch.ones(ci.numel(), dtype=torch.bool, device=dev)
+            mask[hot] = False
+            new_order = torch.cat([hot, torch.nonzero(mask).flatten()])
+            inv = torch.empty_like(new_order)
+            inv[new_order] = torch.arange(new_order.numel(), device=dev)
+            ri = inv[ri]
+            self.li = self.li[new_order]
+            ci = ci[new_order]
+        self.li_sorted, self.li_perm = torch.sort(self.li)
         order = torch.argsort(ru, stable=True)
         ru, ri, r = ru[order].to(torch.int32), ri[order].to(torch.int32), r[order]
         del order
@@ -152,10 +175,12 @@ class MfSgdGpu:
         self.nchunks = nch
         # concurrency weights (see csrc/cuda/mf.cu): expected number of resident
         # warps that touch the same row at the same time
-        P = min(self.sgd_blocks * 8, max(nch, 1))
+        P = min(P, max(nch, 1))
         denom = max(nnz, 1)
         self.su = (1.0 / torch.clamp(self.hot_mix * P * cu.to(torch.float32) / denom, min=1.0)).contiguous()
-        self.si = (1.0 / torch.clamp(self.hot_mix * P * ci.to(torch.float32) / denom, min=1.0)).contiguous()
+        conc_i = torch.full((ci.numel(),), float(P), device=dev)
+        conc_i[: self.hot_T] = float(min(self.warps_per_block, P))  # replicas: per-CTA concurrency
+        self.si = (1.0 / torch.clamp(self.hot_mix * conc_i * ci.to(torch.float32) / denom, min=1.0)).contiguous()
         nU, nI = self.lu.numel(), self.li.numel()
         self.Wl = torch.empty(nU, self.D, device=dev)
         self.W0 = torch.empty(nU, self.D, device=dev)
@@ -243,7 +268,8 @@ class MfSgdGpu:
         if self.h_ru is None:
             _lib.call("pcl_mf_sgd_pass", self.ru, self.ri, self.rr, self.ru.numel(), self.Wl,
                       self.Hl, self.bul, self.bil, self.su, self.si, self.D, self.mu,
-                      self.alpha, self.beta, 1, self.sgd_blocks, self.sse, s)
+                      self.alpha, self.beta, self.hot_T, self.chunks_per_flush, 0.0,
+                      self.sgd_blocks, self.sse, s)
         else:
             self._sgd_pass_streamed()
 
@@ -277,8 +303,8 @@ class MfSgdGpu:
             self.h2d_bytes += 12 * m
             main.wait_event(self._copied[b])
             _lib.call("pcl_mf_sgd_pass", bru, bri, brr, m, self.Wl, self.Hl, self.bul, self.bil,
-                      self.su, self.si, self.D, self.mu, self.alpha, self.beta, 1,
-                      self.sgd_blocks, self.sse, main.cuda_stream)
+                      self.su, self.si, self.D, self.mu, self.alpha, self.beta, self.hot_T,
+                      self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, main.cuda_stream)
             self._consumed[b].record(main)
             k += 1
 
@@ -353,8 +379,9 @@ class MfSgdGpu:
         u = u.to(dev, torch.int64)
         i = i.to(dev, torch.int64)
         pu = torch.searchsorted(self.lu, u).clamp(max=max(self.lu.numel() - 1, 0))
-        pi = torch.searchsorted(self.li, i).clamp(max=max(self.li.numel() - 1, 0))
-        ok = (self.lu[pu] == u) & (self.li[pi] == i)
+        pi = torch.searchsorted(self.li_sorted, i).clamp(max=max(self.li.numel() - 1, 0))
+        ok = (self.lu[pu] == u) & (self.li_sorted[pi] == i)
+        pi = self.li_perm[pi]
         pu = torch.where(ok, pu, torch.full_like(pu, -1)).to(torch.int32).contiguous()
         pi = torch.where(ok, pi, torch.full_like(pi, -1)).to(torch.int32).contiguous()
         pred = torch.empty(u.numel(), device=dev)

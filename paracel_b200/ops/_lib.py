@@ -42,7 +42,7 @@ SIGS = {
     "pcl_scalars_push_f32": "ppiqpppip",
     "pcl_rows_pull_i32": "ppiiqppp",
     "pcl_rows_push_i32": "ppiiqppip",
-    "pcl_mf_sgd_pass": "pppqppppppifffqipp",
+    "pcl_mf_sgd_pass": "pppqppppppifffiifipp",
     "pcl_mf_sse": "pppqppppifppp",
     "pcl_ssp_commit": "piiqp",
     "pcl_ssp_wait": "piqQpip",

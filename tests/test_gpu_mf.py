@@ -121,12 +121,12 @@ def test_mf_single_chunk_matches_sequential_oracle():
     from paracel_b200.models.mf_gpu import MfSgdGpu
     dev = "cuda:0"
     g = torch.Generator().manual_seed(3)
-    for k in (32, 80, 128):
+    for k, hot in ((32, 64), (80, 64), (128, 64), (128, 0), (64, 3)):
         nu, ni, nnz = 6, 9, 31
         u = torch.randint(0, nu, (nnz,), generator=g)
         i = torch.randint(0, ni, (nnz,), generator=g)
         r = torch.randint(1, 6, (nnz,), generator=g).float()
-        m = MfSgdGpu(nu, ni, k=k, alpha=0.05, beta=0.02, rounds=1, device=dev)
+        m = MfSgdGpu(nu, ni, k=k, alpha=0.05, beta=0.02, rounds=1, device=dev, hot_rows=hot)
         m.load_ratings(u, i, r)
         m.init_parameters()
         assert torch.all(m.su == 1) and torch.all(m.si == 1)
