@@ -1,0 +1,56 @@
+"""Constants and small container types (reference: include/paracel_types.hpp:43-61
+constants, 256-304 ``bag_type``)."""
+from __future__ import annotations
+
+from typing import Callable, Generic, Iterable, Iterator, List, TypeVar
+
+BLK_SZ = 32            # byte blocks per worker for the map-style load patterns
+THREADS_NUM = 5        # op classes of a client connection set
+SEPERATOR = "_PARACEL_"          # separator of server endpoint lists (spelling as in the reference)
+SEPERATOR_INNER = "_ps_"
+DEFAULT_PORT = 11777
+SENTINEL = 2147483648  # "no out-link" marker in PageRank inputs (pr.hpp:28)
+
+T = TypeVar("T")
+
+
+class bag_type(Generic[T]):
+    """A growable bag of items with ``put``, ``get`` (copy), ``traverse`` and iteration."""
+
+    def __init__(self, items: Iterable[T] = ()):
+        self.c: List[T] = list(items)
+
+    def put(self, item: T) -> None:
+        self.c.append(item)
+
+    def get(self) -> "bag_type[T]":
+        return bag_type(self.c)
+
+    def is_empty(self) -> bool:
+        return not self.c
+
+    def size(self) -> int:
+        return len(self.c)
+
+    def __len__(self) -> int:
+        return len(self.c)
+
+    def traverse(self, func: Callable[[T], None]) -> None:
+        for x in self.c:
+            func(x)
+
+    def __iter__(self) -> Iterator[T]:
+        return iter(self.c)
+
+    def assign(self, other: "bag_type[T]") -> "bag_type[T]":
+        """Copy-assignment that returns ``self`` (the reference's operator= forgets to)."""
+        self.c = list(other.c)
+        return self
+
+
+def is_atomic(v) -> bool:
+    return isinstance(v, (bool, int, float, str))
+
+
+def is_seqic(v) -> bool:
+    return isinstance(v, (list, tuple)) and all(isinstance(x, (int, float)) for x in v)
