@@ -37,6 +37,8 @@ def _worker_main(rank: int, world: int, master_port: int, server_info: str, targ
         os.environ.setdefault("OMP_NUM_THREADS", "1")
         import torch
         torch.set_num_threads(1)
+        if "nccl" in backend and torch.cuda.is_available():
+            torch.cuda.set_device(rank % torch.cuda.device_count())
         from ..parallel.comm import Comm, main_env
         env = main_env(backend=backend, timeout_s=float(os.environ.get("PCL_PG_TIMEOUT_S", "300")))
         comm = Comm()

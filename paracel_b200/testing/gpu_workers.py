@@ -1,0 +1,132 @@
+"""Worker bodies of the multi-GPU tests (run as child processes, one per GPU,
+by ``paracel_b200.launch.local.LocalJob``)."""
+from __future__ import annotations
+
+import math
+import time
+
+import torch
+import torch.distributed as dist
+
+
+def symm_and_rows(comm, server_info):
+    from paracel_b200.parallel.symm import SymmBuffer
+    from paracel_b200.ps.tables import RowTable, ScalarTable
+    rank, world = comm.get_rank(), comm.get_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = {}
+    # --- peer-visible buffer: everybody writes its rank into its own buffer, reads the peers'
+    b = SymmBuffer(1024, torch.float32)
+    b.local.fill_(float(rank + 1))
+    torch.cuda.synchronize()
+    comm.synchronize()
+    out["peer_vals"] = [float(b.peer_view(r)[5].item()) for r in range(world)]
+    comm.synchronize()
+    b.free()
+    # --- row table: pull rows owned by every rank, push weighted deltas, check owners
+    rows, width = 1000, 128
+    t = RowTable(rows, width, torch.float32)
+    own = t.owned_ids()
+    t.shard[: own.numel()] = own.to(torch.float32)[:, None] * 0.001 + torch.arange(width, device=dev)[None, :]
+    torch.cuda.synchronize()
+    comm.synchronize()
+    g = torch.Generator(device=dev)
+    g.manual_seed(100 + rank)
+    ids = torch.unique(torch.randint(0, rows, (400,), device=dev, generator=g))
+    cur = torch.empty(ids.numel(), width, device=dev)
+    old = torch.empty_like(cur)
+    t.pull(ids, cur, old)
+    torch.cuda.synchronize()
+    exp = ids.to(torch.float32)[:, None] * 0.001 + torch.arange(width, device=dev)[None, :]
+    out["pull_ok"] = bool(torch.allclose(cur, exp))
+    comm.synchronize()
+    cur += 1.0  # every holder adds one
+    wgt = torch.full((ids.numel(),), 0.5, device=dev)
+    t.push(ids, cur, old, wgt)
+    torch.cuda.synchronize()
+    comm.synchronize()
+    # holders per row
+    cnt = torch.zeros(rows, device=dev)
+    cnt[ids] = 1.0
+    dist.all_reduce(cnt)
+    own_exp = own.to(torch.float32)[:, None] * 0.001 + torch.arange(width, device=dev)[None, :] \
+        + 0.5 * cnt[own][:, None]
+    out["push_ok"] = bool(torch.allclose(t.shard[: own.numel()], own_exp, atol=1e-5))
+    comm.synchronize()
+    t.free()
+    # --- int rows + scalars
+    ti = RowTable(64, 1024, torch.int32)
+    idsi = torch.arange(0, 64, device=dev)
+    one = torch.ones(64, 1024, dtype=torch.int32, device=dev)
+    ti.push(idsi, one)
+    torch.cuda.synchronize()
+    comm.synchronize()
+    got = torch.empty_like(one)
+    ti.pull(idsi, got)
+    torch.cuda.synchronize()
+    out["int_ok"] = bool(torch.all(got == world))
+    comm.synchronize()
+    ti.free()
+    return out
+
+
+def ssp_clock(comm, server_info):
+    """Rank 1 is slow; rank 0 may run at most `staleness` clocks ahead.  Then rank 1 stops
+    committing (a flag that nothing sets) and rank 0's bounded wait reports a timeout."""
+    from paracel_b200.parallel.ssp_device import DeviceSspClock, SspTimeout
+    rank = comm.get_rank()
+    c = DeviceSspClock(staleness=2, total_iters=100, timeout_s=0.5)
+    comm.synchronize()
+    ahead = []
+    t0 = time.time()
+    for it in range(6):
+        c.wait()
+        c.check()  # raises if the wait gave up
+        torch.cuda.synchronize()
+        mn = int(c.clocks[: c.world].min().item())
+        ahead.append(c.clock - mn)
+        if rank == 1:
+            time.sleep(0.05)
+        c.commit()
+        torch.cuda.synchronize()
+    comm.synchronize()
+    res = {"max_ahead": max(ahead), "timeout": None}
+    # withheld commit: rank 1 stays silent, rank 0 tries to go 3 more clocks
+    if rank == 0:
+        try:
+            for it in range(4):
+                c.wait()
+                c.check()
+                c.commit()
+            res["timeout"] = "none"
+        except SspTimeout as e:
+            res["timeout"] = (e.expected, e.seen)
+        # the context is still usable after the timed-out wait
+        res["alive"] = float(torch.ones(4, device="cuda").sum().item())
+    comm.synchronize()
+    c.free()
+    return res
+
+
+def mf_train(comm, server_info, nu, ni, nnz, k, rounds, staleness):
+    from paracel_b200.models.mf_gpu import MfSgdGpu, balanced_groups
+    from paracel_b200.utils.synth import MfRatingStream
+    rank, world = comm.get_rank(), comm.get_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    st = MfRatingStream(nu, ni, nnz, seed=5, device=dev)
+    u, i, r = st.chunk_at(0)
+    m = MfSgdGpu(nu, ni, k=k, alpha=0.005, beta=0.02, rounds=rounds, staleness=staleness,
+                 ssp=staleness > 0, seed=3)
+    cu = torch.bincount(u, minlength=nu)
+    ci = torch.bincount(i, minlength=ni)
+    ug, ig = balanced_groups(cu, m.npx), balanced_groups(ci, m.npy)
+    keep = (ug[u].to(torch.int64) * m.npy + ig[i].to(torch.int64)) == rank
+    m.load_ratings(u[keep], i[keep], r[keep])
+    m.init_parameters()
+    m.pull()
+    r0 = m.rmse()
+    m.fit()
+    r1 = m.rmse()
+    n_local = int(keep.sum().item())
+    m.free()
+    return {"rmse0": r0, "rmse1": r1, "nnz_local": n_local, "mu": m.mu}
