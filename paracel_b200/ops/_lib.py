@@ -44,6 +44,8 @@ SIGS = {
     "pcl_rows_push_i32": "ppiiqppip",
     "pcl_mf_sgd_pass": "pppqppppppifffiifipp",
     "pcl_mf_sse": "pppqppppifppp",
+    "pcl_gemm_tf32": "pppiiiqipppppiiiiipip",
+    "pcl_split3_tf32": "ppqiip",
     "pcl_ssp_commit": "piiqp",
     "pcl_ssp_wait": "piqQpip",
 }

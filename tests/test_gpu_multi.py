@@ -49,3 +49,12 @@ def test_mf_two_ranks_converges_like_one_rank():
     assert abs(two[0]["rmse1"] - two[1]["rmse1"]) < 1e-6  # all-reduced metric
     assert two[0]["rmse1"] < two[0]["rmse0"]
     assert abs(two[0]["rmse1"] - one[0]["rmse1"]) < 0.05 * one[0]["rmse1"]
+
+
+@needs2
+def test_fused_allgather_gemm_two_ranks():
+    from paracel_b200.testing.gpu_workers import fused_gather_gemm
+    res = _job(2).run(fused_gather_gemm, (1000, 64, 900), timeout_s=300)
+    for r in res:
+        assert r["err0"] < 5e-3 and r["err1"] < 5e-3, r
+        assert r["argmin_ok"]
