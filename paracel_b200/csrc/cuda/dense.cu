@@ -1,0 +1,205 @@
+// Dense parameter vectors sharded by range over the ranks ("theta"-style keys).
+//
+//   dense_read     all-gather: every rank copies all shards into a local full
+//                  vector with 128-bit peer loads (paracel_read of a dense key,
+//                  reference include/ps.hpp:437-462 + one TCP round trip).
+//   dense_bupdate  reduce-scatter fused with the registered update handler:
+//                  the owner of a slice sums that slice of every rank's delta
+//                  vector straight out of peer memory and applies
+//                      add       theta += sum                    (lr_theta_update, default_incr_*)
+//                      sgd       theta -= lr * sum
+//                      prox_l1   w = theta - lr * sum; theta = sign(w) max(|w| - lr*lambda, 0)
+//                      max       theta = max(theta, max_r delta_r)
+//                  (paracel_bupdate + server-side handler, ps.hpp:779-798,
+//                  include/server.hpp:88-100, 331-349).
+//   publish        release-store of an epoch number into slot [rank] of every
+//                  peer's flag array (delta ready / update done).
+// Both kernels start with a bounded wait on a local flag array that the peers
+// publish into; the last block of dense_bupdate publishes "done".
+#include "common.cuh"
+
+namespace {
+
+enum DenseHandler { DH_ADD = 0, DH_SGD = 1, DH_PROX_L1 = 2, DH_MAX = 3 };
+
+struct ReadArgs {
+  const float* const* shards;  // world pointers, shard r = elements [r*S, (r+1)*S)
+  float* out;                  // full vector, L floats
+  long long L, S;
+  int world, rank;
+  const long long* flags;      // wait for min(flags[0..world)) >= target (null: no wait)
+  long long target;
+  unsigned long long timeout_ns;
+  PclStatus* status;
+};
+
+__global__ void __launch_bounds__(256) dense_read_kernel(ReadArgs a) {
+  __shared__ int ok;
+  if (a.flags != nullptr && a.target > 0) {
+    if (threadIdx.x == 0)
+      ok = pcl_wait_min_clock(a.flags, a.world, a.target, a.timeout_ns, a.status, a.rank, 20) ? 1 : 0;
+    __syncthreads();
+    if (!ok) return;
+  }
+  const long long nvec = a.L >> 2;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  for (long long v = tid; v < nvec; v += nth) {
+    const long long e = v << 2;
+    // visit the shards in ring order starting from this rank to spread the switch load
+    int owner = (int)(e / a.S);
+    if (owner >= a.world) owner = a.world - 1;
+    const float* src = a.shards[owner] + (e - (long long)owner * a.S);
+    const float4 x = pcl_ld_sys4(src);
+    *reinterpret_cast<float4*>(a.out + e) = x;
+  }
+  for (long long e = (nvec << 2) + tid; e < a.L; e += nth) {
+    int owner = (int)(e / a.S);
+    if (owner >= a.world) owner = a.world - 1;
+    a.out[e] = a.shards[owner][e - (long long)owner * a.S];
+  }
+}
+
+struct BupArgs {
+  float* theta;                 // this rank's shard, S floats (elements [rank*S, ...))
+  const float* const* deltas;   // world pointers to full-length delta vectors (L floats each)
+  long long L, S;
+  int world, rank;
+  int handler;
+  float lr, lambda;
+  const long long* ready;       // local flag array the peers publish "delta ready" into
+  long long epoch;
+  unsigned long long timeout_ns;
+  PclStatus* status;
+  long long* const* done_ptrs;  // world pointers to every rank's "done" array (may be null)
+  unsigned int* block_counter;  // zero-initialised, reset by the last block
+  double* nnz_out;              // optional: += number of non-zero entries of the new shard
+};
+
+__device__ __forceinline__ float apply_handler(int handler, float th, float sum, float mx, float lr,
+                                               float lambda) {
+  switch (handler) {
+    case DH_ADD: return th + sum;
+    case DH_SGD: return th - lr * sum;
+    case DH_PROX_L1: {
+      const float w = th - lr * sum;
+      const float t = lr * lambda;
+      return w > t ? w - t : (w < -t ? w + t : 0.f);
+    }
+    default: return fmaxf(th, mx);
+  }
+}
+
+__global__ void __launch_bounds__(256) dense_bupdate_kernel(BupArgs a) {
+  __shared__ int ok;
+  if (a.ready != nullptr && a.epoch > 0) {
+    if (threadIdx.x == 0)
+      ok = pcl_wait_min_clock(a.ready, a.world, a.epoch, a.timeout_ns, a.status, a.rank, 21) ? 1 : 0;
+    __syncthreads();
+    if (!ok) return;
+  }
+  const long long lo = (long long)a.rank * a.S;
+  long long n = a.L - lo;
+  if (n > a.S) n = a.S;
+  if (n < 0) n = 0;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  const bool vec_ok = ((lo & 3) == 0);
+  const long long nvec = vec_ok ? (n >> 2) : 0;
+  float nz = 0.f;
+  for (long long v = tid; v < nvec; v += nth) {
+    const long long e = v << 2;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 m = make_float4(-3.4e38f, -3.4e38f, -3.4e38f, -3.4e38f);
+    for (int i = 0; i < a.world; ++i) {
+      int r = a.rank + i;
+      if (r >= a.world) r -= a.world;
+      const float4 d = pcl_ld_sys4(a.deltas[r] + lo + e);
+      s.x += d.x; s.y += d.y; s.z += d.z; s.w += d.w;
+      m.x = fmaxf(m.x, d.x); m.y = fmaxf(m.y, d.y); m.z = fmaxf(m.z, d.z); m.w = fmaxf(m.w, d.w);
+    }
+    float4 t = *reinterpret_cast<float4*>(a.theta + e);
+    t.x = apply_handler(a.handler, t.x, s.x, m.x, a.lr, a.lambda);
+    t.y = apply_handler(a.handler, t.y, s.y, m.y, a.lr, a.lambda);
+    t.z = apply_handler(a.handler, t.z, s.z, m.z, a.lr, a.lambda);
+    t.w = apply_handler(a.handler, t.w, s.w, m.w, a.lr, a.lambda);
+    *reinterpret_cast<float4*>(a.theta + e) = t;
+    nz += (t.x != 0.f) + (t.y != 0.f) + (t.z != 0.f) + (t.w != 0.f);
+  }
+  for (long long e = (nvec << 2) + tid; e < n; e += nth) {
+    float s = 0.f, m = -3.4e38f;
+    for (int i = 0; i < a.world; ++i) {
+      int r = a.rank + i;
+      if (r >= a.world) r -= a.world;
+      float d;
+      asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(d) : "l"(a.deltas[r] + lo + e));
+      s += d;
+      m = fmaxf(m, d);
+    }
+    const float t = apply_handler(a.handler, a.theta[e], s, m, a.lr, a.lambda);
+    a.theta[e] = t;
+    nz += (t != 0.f);
+  }
+  if (a.nnz_out != nullptr) {
+    nz = pcl_warp_sum(nz);
+    if ((threadIdx.x & 31) == 0 && nz != 0.f) atomicAdd(a.nnz_out, (double)nz);
+  }
+  // the last block to finish publishes "done" to every rank
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(a.block_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *a.block_counter = 0u;
+      if (a.done_ptrs != nullptr) {
+        __threadfence_system();
+        for (int r = 0; r < a.world; ++r) pcl_st_release_sys(a.done_ptrs[r] + a.rank, a.epoch);
+      }
+    }
+  }
+}
+
+__global__ void publish_kernel(long long* const* flag_ptrs, int world, int rank, long long value) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    __threadfence_system();
+    pcl_st_release_sys(flag_ptrs[r] + rank, value);
+  }
+}
+
+}  // namespace
+
+PCL_API int pcl_dense_read(const float* const* shards, float* out, long long L, long long S,
+                           int world, int rank, const long long* flags, long long target,
+                           unsigned long long timeout_ns, PclStatus* status, cudaStream_t stream) {
+  if (L <= 0) return 0;
+  if ((S & 3) && world > 1) return (int)cudaErrorInvalidValue;  // shards must keep 16-byte alignment
+  ReadArgs a{shards, out, L, S, world, rank, flags, target, timeout_ns, status};
+  long long blocks = (L / 4 + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  dense_read_kernel<<<(int)blocks, 256, 0, stream>>>(a);
+  return pcl_last_error();
+}
+
+PCL_API int pcl_dense_bupdate(float* theta, const float* const* deltas, long long L, long long S,
+                              int world, int rank, int handler, float lr, float lambda,
+                              const long long* ready, long long epoch, unsigned long long timeout_ns,
+                              PclStatus* status, long long* const* done_ptrs,
+                              unsigned int* block_counter, double* nnz_out, cudaStream_t stream) {
+  if (L <= 0) return 0;
+  BupArgs a{theta, deltas, L, S, world, rank, handler, lr, lambda, ready, epoch, timeout_ns,
+            status, done_ptrs, block_counter, nnz_out};
+  long long blocks = (S / 4 + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  dense_bupdate_kernel<<<(int)blocks, 256, 0, stream>>>(a);
+  return pcl_last_error();
+}
+
+PCL_API int pcl_publish_flag(long long* const* flag_ptrs, int world, int rank, long long value,
+                             cudaStream_t stream) {
+  if (world > 1024) return (int)cudaErrorInvalidValue;
+  publish_kernel<<<1, ((world + 31) / 32) * 32, 0, stream>>>(flag_ptrs, world, rank, value);
+  return pcl_last_error();
+}

@@ -1,0 +1,196 @@
+// Gradient kernels of the linear models (logistic regression, ridge, sparse
+// L1-regularised logistic regression / Lasso).
+//
+// Math (reference: alg/classification/logistic_regression/lr.cpp:69-72, 119-145;
+// alg/regression/ridge/ridge.hpp:73-96; tool/lr_l1_serial.cpp:46-73 for the L1
+// objective): residual r = y - h(theta.x) with h = sigmoid (logistic) or identity
+// (ridge), gradient accumulator g = sum_rows r * x, loss = log-loss or squared error.
+// The accumulated g is what the reference's "dgd" method pushes with one bupdate per
+// round; here it is written straight into the delta vector that dense_bupdate reduces.
+//
+// Dense kernel: one warp per row, theta cached in shared memory, per-block partial
+// gradient in shared memory, then a two-stage reduction through a scratch buffer
+// (blocks x d partials, summed in block order by the last block) so that the result
+// does not depend on atomics between blocks.
+// Sparse kernel: CSR rows, one warp per row; features with index < hot_T (the most
+// frequent ones after frequency renumbering) accumulate in shared memory per block,
+// the others go to global memory with red.add.
+#include "common.cuh"
+
+namespace {
+
+struct DenseGradArgs {
+  const float* X;      // n x d row-major
+  const float* y;      // n
+  const float* theta;  // d
+  long long n;
+  int d;
+  int logistic;
+  float* g;            // d, written (not accumulated)
+  double* loss;        // 1, written
+  float* scratch;      // gridDim.x * d partial gradients + gridDim.x loss partials (as 2 floats each)
+  unsigned int* counter;  // zero before the first launch; the last block resets it
+};
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + __expf(-z)); }
+
+__global__ void __launch_bounds__(256) dense_grad_kernel(DenseGradArgs a) {
+  extern __shared__ float sm[];
+  float* s_theta = sm;          // d
+  float* s_g = sm + a.d;        // d
+  __shared__ double s_loss[8];
+  __shared__ int is_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  for (int j = threadIdx.x; j < a.d; j += blockDim.x) {
+    s_theta[j] = a.theta[j];
+    s_g[j] = 0.f;
+  }
+  __syncthreads();
+  double loss = 0.0;
+  for (long long row = (long long)blockIdx.x * wpb + warp; row < a.n; row += (long long)gridDim.x * wpb) {
+    const float* x = a.X + row * a.d;
+    float z = 0.f;
+    for (int j = lane; j < a.d; j += 32) z = fmaf(x[j], s_theta[j], z);
+    z = pcl_warp_sum(z);
+    const float yy = a.y[row];
+    float r;
+    if (a.logistic) {
+      const float h = sigmoidf_(z);
+      r = yy - h;
+      // log-loss with clamping so that a saturated sigmoid does not give inf
+      const float hc = fminf(fmaxf(h, 1e-7f), 1.f - 1e-7f);
+      loss += (yy == 1.f) ? -(double)__logf(hc) : -(double)__logf(1.f - hc);
+    } else {
+      r = yy - z;
+      loss += (double)r * (double)r;
+    }
+    for (int j = lane; j < a.d; j += 32) atomicAdd(&s_g[j], r * x[j]);
+  }
+  if (lane == 0) s_loss[warp] = loss;  // identical in every lane of the warp
+  __syncthreads();
+  float* part = a.scratch + (long long)blockIdx.x * a.d;
+  for (int j = threadIdx.x; j < a.d; j += blockDim.x) part[j] = s_g[j];
+  if (threadIdx.x == 0) {
+    double l = 0.0;
+    for (int w = 0; w < wpb; ++w) l += s_loss[w];
+    reinterpret_cast<double*>(a.scratch + (((long long)gridDim.x * a.d + 1) & ~1LL))[blockIdx.x] = l;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(a.counter, 1u);
+    is_last = (prev == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int j = threadIdx.x; j < a.d; j += blockDim.x) {
+    float s = 0.f;
+    for (unsigned int b = 0; b < gridDim.x; ++b) s += __ldcg(a.scratch + (long long)b * a.d + j);
+    a.g[j] = s;
+  }
+  if (threadIdx.x == 0) {
+    const double* lp = reinterpret_cast<const double*>(a.scratch + (((long long)gridDim.x * a.d + 1) & ~1LL));
+    double l = 0.0;
+    for (unsigned int b = 0; b < gridDim.x; ++b) l += __ldcg(lp + b);
+    *a.loss = l;
+    *a.counter = 0u;
+  }
+}
+
+struct SparseGradArgs {
+  const long long* row_ptr;  // n + 1
+  const int* cols;
+  const float* vals;         // null: all ones
+  const float* y;
+  const float* theta;        // full local copy
+  long long n;
+  int logistic;
+  int hot_T;                 // feature ids < hot_T accumulate in shared memory
+  float* g;                  // accumulated into (caller zeroes it)
+  double* loss;              // accumulated into
+};
+
+__global__ void __launch_bounds__(256) sparse_grad_kernel(SparseGradArgs a) {
+  extern __shared__ float s_hot[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  for (int j = threadIdx.x; j < a.hot_T; j += blockDim.x) s_hot[j] = 0.f;
+  __syncthreads();
+  double loss = 0.0;
+  for (long long row = (long long)blockIdx.x * wpb + warp; row < a.n; row += (long long)gridDim.x * wpb) {
+    const long long b = a.row_ptr[row], e = a.row_ptr[row + 1];
+    float z = 0.f;
+    for (long long p = b + lane; p < e; p += 32) {
+      const float v = a.vals ? a.vals[p] : 1.f;
+      z = fmaf(v, __ldg(a.theta + a.cols[p]), z);
+    }
+    z = pcl_warp_sum(z);
+    const float yy = a.y[row];
+    float r;
+    if (a.logistic) {
+      const float h = sigmoidf_(z);
+      r = yy - h;
+      const float hc = fminf(fmaxf(h, 1e-7f), 1.f - 1e-7f);
+      loss += (yy == 1.f) ? -(double)__logf(hc) : -(double)__logf(1.f - hc);
+    } else {
+      r = yy - z;
+      loss += (double)r * (double)r;
+    }
+    for (long long p = b + lane; p < e; p += 32) {
+      const int c = a.cols[p];
+      const float v = a.vals ? a.vals[p] : 1.f;
+      if (c < a.hot_T) atomicAdd(&s_hot[c], r * v);
+      else atomicAdd(a.g + c, r * v);
+    }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < a.hot_T; j += blockDim.x) {
+    const float v = s_hot[j];
+    if (v != 0.f) atomicAdd(a.g + j, v);
+  }
+  if (lane == 0 && loss != 0.0) atomicAdd(a.loss, loss);
+}
+
+}  // namespace
+
+// Number of floats of scratch the dense gradient needs for `blocks` blocks and dimension d.
+PCL_API long long pcl_lr_dense_scratch_floats(int blocks, int d) {
+  return (long long)blocks * d + 2LL * blocks + 4;
+}
+
+// g[d] = sum_rows (y - h(theta.x)) x, *loss = summed loss.  `scratch` must hold
+// pcl_lr_dense_scratch_floats(blocks, d) floats (8-byte aligned); `counter` is one
+// zero-initialised unsigned int that the kernel leaves at zero.  d <= 12000.
+PCL_API int pcl_lr_dense_grad(const float* X, const float* y, const float* theta, long long n, int d,
+                              int logistic, float* g, double* loss, float* scratch,
+                              unsigned int* counter, int blocks, cudaStream_t stream) {
+  if (n <= 0 || d <= 0) return (int)cudaErrorInvalidValue;
+  if (d > 12000) return (int)cudaErrorInvalidValue;
+  if (blocks <= 0) blocks = 148 * 2;
+  long long need = (n + 7) / 8;
+  if (need < blocks) blocks = (int)need;
+  DenseGradArgs a{X, y, theta, n, d, logistic, g, loss, scratch, counter};
+  size_t smem = 2 * (size_t)d * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(dense_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dense_grad_kernel<<<blocks, 256, smem, stream>>>(a);
+  return pcl_last_error();
+}
+
+PCL_API int pcl_lr_sparse_grad(const long long* row_ptr, const int* cols, const float* vals,
+                               const float* y, const float* theta, long long n, int logistic,
+                               int hot_T, float* g, double* loss, int blocks, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (hot_T < 0 || hot_T > 24 * 1024) return (int)cudaErrorInvalidValue;
+  if (blocks <= 0) blocks = 148 * 4;
+  long long need = (n + 7) / 8;
+  if (need < blocks) blocks = (int)need;
+  SparseGradArgs a{row_ptr, cols, vals, y, theta, n, logistic, hot_T, g, loss};
+  size_t smem = (size_t)hot_T * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(sparse_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  sparse_grad_kernel<<<blocks, 256, smem, stream>>>(a);
+  return pcl_last_error();
+}

@@ -46,6 +46,12 @@ SIGS = {
     "pcl_mf_sse": "pppqppppifppp",
     "pcl_gemm_tf32": "pppiiiqipppppiiiiipip",
     "pcl_split3_tf32": "ppqiip",
+    "pcl_dense_read": "ppqqiipqQpp",
+    "pcl_dense_bupdate": "ppqqiiiffpqQppppp",
+    "pcl_publish_flag": "piiqp",
+    "pcl_lr_dense_grad": "pppqiippppip",
+    "pcl_lr_sparse_grad": "pppppqiippip",
+    "pcl_pagerank_pull": "ppppqfppppip",
     "pcl_ssp_commit": "piiqp",
     "pcl_ssp_wait": "piqQpip",
 }

@@ -108,3 +108,99 @@ class ScalarTable:
     def free(self):
         self.shard = None
         self.buf.free()
+
+
+DENSE_HANDLERS = {"add": 0, "sgd": 1, "prox_l1": 2, "max": 3,
+                  # handler names of the reference that are plain adds
+                  "lr_theta_update": 0, "ridge_theta_update": 0, "default_incr_ld": 0,
+                  "default_incr_lf": 0, "svd_updater": 0, "local_update_kmeans_clusters": 0}
+
+
+class DenseTable:
+    """One dense fp32 parameter vector of length ``L`` ("theta", cluster centres, a rank
+    vector), range-sharded over the ranks: rank r owns elements ``[r*S, (r+1)*S)``.
+
+    ``read()`` is ``paracel_read`` of the key: an all-gather into a local full copy by peer
+    loads.  ``delta()`` is the local full-length buffer a gradient kernel writes into, and
+    ``bupdate()`` is ``paracel_bupdate`` with the table's registered handler: every owner
+    reduces its slice of all ranks' delta buffers out of peer memory and applies the handler
+    in the same kernel (reduce-scatter fused with the update).  Ordering between ranks is
+    carried by two flag arrays in peer memory ("delta ready", "update done") that the kernels
+    wait on with a deadline; no host barrier is involved.
+    """
+
+    def __init__(self, L: int, group=None, device=None, handler: str = "add", lr: float = 1.0,
+                 lam: float = 0.0, timeout_s: float = 5.0):
+        import torch.distributed as dist
+        self.L = int(L)
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        S = (self.L + self.world - 1) // self.world
+        self.S = (S + 3) // 4 * 4
+        self.Lp = self.S * self.world
+        self.theta_buf = SymmBuffer(self.S, torch.float32, group, device)
+        self.delta_buf = SymmBuffer(2 * self.Lp, torch.float32, group, device)
+        self.flag_buf = SymmBuffer(128, torch.int64, group, device)
+        self.device = self.theta_buf.device
+        self.shard = self.theta_buf.local
+        self.full = torch.zeros(self.Lp, device=self.device)
+        self.handler, self.lr, self.lam = handler, float(lr), float(lam)
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.epoch = 0
+        self.status = torch.zeros(4, dtype=torch.int64, device=self.device)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.nnz = torch.zeros(1, dtype=torch.float64, device=self.device)
+        base = self.delta_buf.ptr_table
+        self._delta_tables = [base.clone(), (base + self.Lp * 4).contiguous()]
+        self._ready_table = self.flag_buf.ptr_table.clone()
+        self._done_table = (self.flag_buf.ptr_table + 64 * 8).contiguous()
+        self.ready = self.flag_buf.local[:64]
+        self.done = self.flag_buf.local[64:]
+
+    def owned_range(self):
+        lo = self.rank * self.S
+        return lo, min(self.L, lo + self.S)
+
+    def delta(self) -> torch.Tensor:
+        """Buffer (length L) for the delta of the NEXT bupdate."""
+        b = (self.epoch + 1) & 1
+        return self.delta_buf.local[b * self.Lp: b * self.Lp + self.L]
+
+    def read(self) -> torch.Tensor:
+        _lib.call("pcl_dense_read", self.theta_buf.ptr_table, self.full, self.Lp, self.S, self.world,
+                  self.rank, self.done, self.epoch, self.timeout_ns, self.status, _lib.stream_ptr())
+        return self.full[: self.L]
+
+    def bupdate(self, handler: Optional[str] = None, lr: Optional[float] = None,
+                lam: Optional[float] = None, count_nnz: bool = False):
+        self.epoch += 1
+        b = self.epoch & 1
+        s = _lib.stream_ptr()
+        _lib.call("pcl_publish_flag", self._ready_table, self.world, self.rank, self.epoch, s)
+        h = DENSE_HANDLERS[handler or self.handler]
+        if count_nnz:
+            self.nnz.zero_()
+        _lib.call("pcl_dense_bupdate", self.shard, self._delta_tables[b], self.Lp, self.S, self.world,
+                  self.rank, h, self.lr if lr is None else float(lr),
+                  self.lam if lam is None else float(lam), self.ready, self.epoch, self.timeout_ns,
+                  self.status, self._done_table, self.counter, self.nnz if count_nnz else None, s)
+
+    def write(self, values: torch.Tensor):
+        """Owner-side initialisation from a full vector that every rank passes identically."""
+        lo, hi = self.owned_range()
+        self.shard.zero_()
+        if hi > lo:
+            self.shard[: hi - lo] = values[lo:hi].to(self.device, torch.float32)
+
+    def check(self):
+        st = self.status.cpu()
+        if int(st[0].item()) & 0xFFFFFFFF:
+            self.status.zero_()
+            raise RuntimeError(f"dense table wait timed out (wait id {int(st[1].item()) & 0xFFFFFFFF}: "
+                               f"expected {int(st[2])}, saw {int(st[3])})")
+
+    def free(self):
+        self.shard = None
+        self.ready = self.done = None
+        for b in (self.theta_buf, self.delta_buf, self.flag_buf):
+            b.free()

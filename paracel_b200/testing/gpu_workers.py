@@ -165,3 +165,38 @@ def fused_gather_gemm(comm, server_info, N, K, M):
     comm.synchronize()
     op.free()
     return out
+
+
+def dense_table_two_ranks(comm, server_info):
+    """Reduce-scatter + handler across ranks without any host barrier between rounds."""
+    from paracel_b200.ps.tables import DenseTable
+    rank, world = comm.get_rank(), comm.get_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    L = 10007
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    theta0 = torch.randn(L, device=dev, generator=g)
+    t = DenseTable(L, handler="prox_l1", lr=0.05, lam=0.3)
+    t.write(theta0)
+    torch.cuda.synchronize()
+    comm.synchronize()
+    exp = theta0.clone()
+    ok = True
+    for it in range(5):
+        cur = t.read()
+        ok = ok and bool(torch.allclose(cur, exp, atol=1e-5))
+        ds = []
+        for r in range(world):
+            g.manual_seed(1000 * it + r)
+            ds.append(torch.randn(L, device=dev, generator=g))
+        t.delta().copy_(ds[rank])
+        t.bupdate()
+        w = exp - 0.05 * sum(ds)
+        exp = torch.sign(w) * torch.clamp(w.abs() - 0.05 * 0.3, min=0)
+    cur = t.read()
+    torch.cuda.synchronize()
+    t.check()
+    ok = ok and bool(torch.allclose(cur, exp, atol=1e-5))
+    comm.synchronize()
+    t.free()
+    return ok

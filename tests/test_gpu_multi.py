@@ -58,3 +58,9 @@ def test_fused_allgather_gemm_two_ranks():
     for r in res:
         assert r["err0"] < 5e-3 and r["err1"] < 5e-3, r
         assert r["argmin_ok"]
+
+
+@needs2
+def test_dense_table_reduce_scatter_handler_two_ranks():
+    from paracel_b200.testing.gpu_workers import dense_table_two_ranks
+    assert all(_job(2).run(dense_table_two_ranks, timeout_s=300))
