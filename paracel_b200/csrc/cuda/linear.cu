@@ -15,7 +15,10 @@
 // Sparse kernel: CSR rows, one warp per row; features with index < hot_T (the most
 // frequent ones after frequency renumbering) accumulate in shared memory per block,
 // the others go to global memory with red.add.
+#include <stdio.h>
+
 #include "common.cuh"
+#include "pcl_noalloc.h"
 
 namespace {
 
@@ -192,5 +195,90 @@ PCL_API int pcl_lr_sparse_grad(const long long* row_ptr, const int* cols, const 
                                        (int)smem);
   if (e != cudaSuccess) return (int)e;
   sparse_grad_kernel<<<blocks, 256, smem, stream>>>(a);
+  return pcl_last_error();
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the dense gradient (declared in pcl_noalloc.h).
+//
+// Some hosts of this library may not call cudaMalloc at all: a serving process
+// that handed its whole HBM budget to one arena at start-up, a plug-in that runs
+// inside somebody else's memory pool, or a latency-critical loop where the
+// implicit device synchronisation of cudaMalloc/cudaFree is not acceptable.  For
+// them the block partials and the block counter of dense_grad_kernel live in
+// the two file-scope device arrays below instead of a caller-provided scratch
+// tensor.  The price: every GPU that loads this library carries the
+// PCL_NOALLOC_MAX_FLOATS * 4 bytes (4 MiB) until the process exits, and all
+// calls on one device share the array, so two calls that overlap on the GPU
+// (different streams) would overwrite each other's partials.
+static __device__ __align__(256) float g_noalloc_scratch[PCL_NOALLOC_MAX_FLOATS];
+static __device__ __align__(256) unsigned int g_noalloc_counter[64];
+
+namespace {
+struct NoAllocSlot {
+  float* scratch = nullptr;
+  unsigned int* counter = nullptr;
+  bool ready = false;
+};
+NoAllocSlot g_noalloc_slots[64];
+char g_noalloc_msg[256] = "";
+}  // namespace
+
+PCL_API const char* pcl_lr_dense_grad_noalloc_error() { return g_noalloc_msg; }
+
+PCL_API int pcl_lr_dense_grad_noalloc(const float* X, const float* y, const float* theta, long long n,
+                                      int d, int logistic, float* g, double* loss, int blocks,
+                                      cudaStream_t stream) {
+  g_noalloc_msg[0] = 0;
+  if (n <= 0 || d <= 0 || d > 12000) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "pcl_lr_dense_grad_noalloc: need n > 0 and 0 < d <= 12000 (got n=%lld d=%d)", n, d);
+    return (int)cudaErrorInvalidValue;
+  }
+  if (blocks <= 0) blocks = 148 * 2;
+  long long need_blocks = (n + 7) / 8;
+  if (need_blocks < blocks) blocks = (int)need_blocks;
+  const long long need = (long long)blocks * d + 2LL * blocks + 4;
+  if (need > (long long)PCL_NOALLOC_MAX_FLOATS) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg),
+             "pcl_lr_dense_grad_noalloc: %d blocks x d=%d needs %lld floats of scratch, the built-in "
+             "array holds %d; use fewer blocks or pcl_lr_dense_grad with your own scratch",
+             blocks, d, need, (int)PCL_NOALLOC_MAX_FLOATS);
+    return (int)cudaErrorInvalidValue;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "pcl_lr_dense_grad_noalloc: device index %d not supported", dev);
+    return (int)cudaErrorInvalidDevice;
+  }
+  NoAllocSlot& slot = g_noalloc_slots[dev];
+  if (!slot.ready) {
+    // One-time set-up for this device (it is the current device): translate the symbols
+    // into device addresses.  In host code the array names are only stand-ins.
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) {
+      snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "cudaGetSymbolAddress(scratch) failed: %s", cudaGetErrorString(e));
+      return (int)e;
+    }
+    slot.scratch = (float*)p;
+    e = cudaGetSymbolAddress(&p, g_noalloc_counter);
+    if (e != cudaSuccess) {
+      snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "cudaGetSymbolAddress(counter) failed: %s", cudaGetErrorString(e));
+      return (int)e;
+    }
+    slot.counter = (unsigned int*)p;
+    slot.ready = true;
+  }
+  // the counter must start at zero whatever an earlier (possibly aborted) call left behind;
+  // the partials are fully overwritten by the kernel before they are read
+  e = cudaMemsetAsync(slot.counter, 0, sizeof(unsigned int), stream);
+  if (e != cudaSuccess) return (int)e;
+  DenseGradArgs a{X, y, theta, n, d, logistic, g, loss, slot.scratch, slot.counter};
+  size_t smem = 2 * (size_t)d * sizeof(float);
+  e = cudaFuncSetAttribute(dense_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dense_grad_kernel<<<blocks, 256, smem, stream>>>(a);
   return pcl_last_error();
 }
