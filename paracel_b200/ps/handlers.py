@@ -28,8 +28,11 @@ from typing import Any, Callable, Dict, Tuple
 
 from ..utils.packer import pack, unpack
 
+import threading
+
 _PY_CACHE: Dict[Tuple[str, str], Callable] = {}
 _LOCAL: Dict[str, Callable] = {}
+_LOAD_LOCK = threading.Lock()
 
 
 def register_handler(name: str, fn: Callable) -> None:
@@ -39,6 +42,13 @@ def register_handler(name: str, fn: Callable) -> None:
 
 def _load(file: str, func: str) -> Callable:
     key = (file, func)
+    if key in _PY_CACHE:
+        return _PY_CACHE[key]
+    with _LOAD_LOCK:  # server threads may ask for the same file at the same time
+        return _load_locked(file, func, key)
+
+
+def _load_locked(file: str, func: str, key) -> Callable:
     if key in _PY_CACHE:
         return _PY_CACHE[key]
     if func in _LOCAL and not file:
