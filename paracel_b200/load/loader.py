@@ -22,7 +22,7 @@ class loader:
         self.m_comm = comm
         self.parserfunc = parser
         self.pattern = pattern
-        self.mix = mix
+        self.mix = mix or pattern == "fset"  # fset lines are adjacency sets: a b:0.2|c:0.4
 
     def _partition(self) -> partition:
         names = expand(self.filenames)

@@ -241,3 +241,49 @@ def run_lda(comm, server_info, inp, out, k, iters):
     m.save()
     m.close()
     return {"loglik": m.loglik, "V": m.V, "tokens": int(m.T), "sum": int(m.topic_sum.sum())}
+
+
+def run_sim_dense(comm, server_info, inp, out, ktop):
+    from paracel_b200.models.similarity import sim_dense
+    m = sim_dense(comm, server_info, inp, inp, out, simbar=0.0, ktop=ktop)
+    m.solve()
+    m.dump_result()
+    m.close()
+    return m.result
+
+
+def run_sim_sparse(comm, server_info, inp, out, topk):
+    from paracel_b200.models.similarity import sim_sparse_row
+    m = sim_sparse_row(comm, server_info, inp, out, "fsv", topk, sim_bar=0.0)
+    m.solve()
+    m.dump_result()
+    m.close()
+    return {k: [(j, s) for s, j in sorted(h, reverse=True)] for k, h in m.sim_result.items()}
+
+
+def run_adjust_ktop(comm, server_info, rating, sim, out):
+    from paracel_b200.models.adjust_ktop import adjust_ktop_s
+    m = adjust_ktop_s(comm, server_info, rating, "fsv", sim, 1, out)
+    m.solve()
+    r = m.cal_rmse()
+    m.dump_result()
+    m.close()
+    return {"ktop": m.ktop_result, "rmse": r}
+
+
+def run_dtr(comm, server_info, ufac, ifac, out, level):
+    from paracel_b200.models.dtr import decision_tree_builder_factor
+    m = decision_tree_builder_factor(comm, server_info, ufac, ifac, out, "", level, 0, 1)
+    m.solve()
+    m.dump()
+    m.close()
+    return m.trees
+
+
+def run_svd(comm, server_info, inp, out, k):
+    from paracel_b200.models.svd import svd
+    m = svd(comm, server_info, inp, out, k=k, iters=15)
+    m.solve()
+    m.dump_result()
+    m.close()
+    return {"sigma": m.sigma.tolist()}
