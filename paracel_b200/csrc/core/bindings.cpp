@@ -147,6 +147,22 @@ PYBIND11_MODULE(_pcl_core, m) {
         };
       });
 
+  m.def("collect_endpoints", [](const std::string& host, int port, int n, double timeout_s,
+                                py::object on_listening) {
+    std::function<void(int)> cb = nullptr;
+    if (!on_listening.is_none()) {
+      auto fp = std::make_shared<py::object>(on_listening);
+      cb = [fp](int p) { py::gil_scoped_acquire g; (*fp)(p); };
+    }
+    std::vector<std::string> out;
+    {
+      py::gil_scoped_release rel;
+      out = collect_endpoints(host, port, n, timeout_s, nullptr, cb);
+    }
+    return out;
+  }, py::arg("host"), py::arg("port"), py::arg("n"), py::arg("timeout_s") = 60.0,
+     py::arg("on_listening") = py::none());
+
   py::class_<PsConnection>(m, "PsConnection")
       .def(py::init<const std::string&, int, double>(), py::arg("host"), py::arg("port"),
            py::arg("timeout_s") = 0.0)

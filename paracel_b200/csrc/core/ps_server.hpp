@@ -499,6 +499,54 @@ class PsServer {
   bool shutdown_requested_ = false;
 };
 
+// Rendezvous of the launcher with freshly started servers (the role of the reference's
+// paracelrun_cpp_proxy, src/paracelrun_cpp_proxy.cpp:23-35 and include/utils.hpp:58-77):
+// listen on `port`, accept `n` connections, read one "host:port" line from each, answer
+// "done", and return the lines.  Gives up after `timeout_s`.
+inline std::vector<std::string> collect_endpoints(const std::string& host, int port, int n,
+                                                  double timeout_s, int* bound_port = nullptr,
+                                                  std::function<void(int)> on_listening = nullptr) {
+  int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+  if (fd < 0) throw std::runtime_error("socket() failed");
+  int one = 1;
+  setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+  sockaddr_in addr{};
+  addr.sin_family = AF_INET;
+  addr.sin_port = htons((uint16_t)port);
+  if (host.empty() || host == "*") addr.sin_addr.s_addr = INADDR_ANY;
+  else inet_pton(AF_INET, host.c_str(), &addr.sin_addr);
+  if (::bind(fd, (sockaddr*)&addr, sizeof(addr)) != 0 || ::listen(fd, 64) != 0) {
+    ::close(fd);
+    throw std::runtime_error("rendezvous: cannot listen on port " + std::to_string(port));
+  }
+  socklen_t len = sizeof(addr);
+  getsockname(fd, (sockaddr*)&addr, &len);
+  if (bound_port) *bound_port = ntohs(addr.sin_port);
+  if (on_listening) on_listening(ntohs(addr.sin_port));
+  timeval tv;
+  tv.tv_sec = (long)timeout_s;
+  tv.tv_usec = (long)((timeout_s - (long)timeout_s) * 1e6);
+  setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+  std::vector<std::string> out;
+  for (int i = 0; i < n; ++i) {
+    int c = ::accept(fd, nullptr, nullptr);
+    if (c < 0) {
+      ::close(fd);
+      throw std::runtime_error("rendezvous: only " + std::to_string(i) + " of " + std::to_string(n) +
+                               " servers reported in time");
+    }
+    setsockopt(c, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+    std::string line;
+    char ch;
+    while (::recv(c, &ch, 1, 0) == 1 && ch != '\n') line.push_back(ch);
+    send_all(c, "done", 4);
+    ::close(c);
+    out.push_back(line);
+  }
+  ::close(fd);
+  return out;
+}
+
 // Blocking request/reply connection to one server.
 class PsConnection {
  public:

@@ -8,7 +8,7 @@
 //                  vector straight out of peer memory and applies
 //                      add       theta += sum                    (lr_theta_update, default_incr_*)
 //                      sgd       theta -= lr * sum
-//                      prox_l1   w = theta - lr * sum; theta = sign(w) max(|w| - lr*lambda, 0)
+//                      prox_l1   w = theta - lr * sum; theta = sign(w) max(|w| - |lr|*lambda, 0)
 //                      max       theta = max(theta, max_r delta_r)
 //                  (paracel_bupdate + server-side handler, ps.hpp:779-798,
 //                  include/server.hpp:88-100, 331-349).
@@ -83,7 +83,7 @@ __device__ __forceinline__ float apply_handler(int handler, float th, float sum,
     case DH_SGD: return th - lr * sum;
     case DH_PROX_L1: {
       const float w = th - lr * sum;
-      const float t = lr * lambda;
+      const float t = fabsf(lr) * lambda;  // lr may carry a sign / a 1/n factor of the caller's delta
       return w > t ? w - t : (w < -t ? w + t : 0.f);
     }
     default: return fmaxf(th, mx);

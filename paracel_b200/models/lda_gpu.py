@@ -1,0 +1,166 @@
+"""LDA by collapsed Gibbs sampling on GPUs with the word-topic counts in HBM (device path
+of alg/topic_model/gLDA.hpp:40-500).
+
+The int32 word-topic table (V x K) is a ``RowTable`` sharded over the ranks, the topic sums a
+one-row table.  Documents are processed in minibatches; one minibatch step is
+
+    wait for the SSP bound               -> DeviceSspClock.wait
+    pull the rows of the batch's words   -> RowTable.pull  (sparse keyed pull, peer loads)
+    one Gibbs sweep over the batch       -> pcl_lda_gibbs  (one warp per document)
+    push (current - pulled) row deltas   -> RowTable.push  (integer reductions at the owner)
+    iter_commit                          -> DeviceSspClock.commit
+
+which is the reference's push-deltas / sync / pull cycle (gLDA.hpp:429-443) made sparse per
+minibatch and bounded-stale instead of bulk synchronous."""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..parallel.ssp_device import DeviceSspClock
+from ..ps.tables import RowTable
+
+
+class LdaGibbsGpu:
+    def __init__(self, vocab: int, k_topics: int = 1024, alpha: Optional[float] = None,
+                 beta: float = 0.01, iters: int = 10, nbatch: int = 4, staleness: int = 2,
+                 group=None, device=None, seed: int = 0, timeout_s: float = 10.0):
+        if k_topics not in (128, 256, 512, 1024):
+            raise ValueError("k_topics must be 128, 256, 512 or 1024")
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.V, self.K = int(vocab), int(k_topics)
+        self.alpha = 50.0 / self.K if alpha is None else float(alpha)
+        self.beta = float(beta)
+        self.iters, self.nbatch, self.seed = int(iters), max(1, int(nbatch)), seed
+        self.wt = RowTable(self.V, self.K, torch.int32, group, device)
+        self.ts = RowTable(1, self.K, torch.int32, group, device)
+        self.device = self.wt.device
+        self.clock = DeviceSspClock(staleness, self.iters * self.nbatch, group, self.device, timeout_s)
+        self.ll = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self._zero_id = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self.step_no = 0
+
+    def load_docs(self, doc_ptr: torch.Tensor, words: torch.Tensor):
+        """This rank's documents as CSR: ``doc_ptr`` (int64, n_docs + 1) and global word ids."""
+        dev, K = self.device, self.K
+        doc_ptr = doc_ptr.to(dev, torch.int64).contiguous()
+        words = words.to(dev, torch.int64).contiguous()
+        self.n_docs = doc_ptr.numel() - 1
+        self.T = int(words.numel())
+        self.doc_len = (doc_ptr[1:] - doc_ptr[:-1]).to(torch.int32).contiguous()
+        g = torch.Generator(device=dev)
+        g.manual_seed(self.seed * 104729 + 13 + self.rank)
+        self.z = torch.randint(0, K, (self.T,), device=dev, generator=g, dtype=torch.int32)
+        doc_of = torch.repeat_interleave(torch.arange(self.n_docs, device=dev), self.doc_len.long())
+        self.n_dk = torch.zeros(self.n_docs, K, dtype=torch.int32, device=dev)
+        self.n_dk.view(-1).index_add_(0, doc_of * K + self.z.long(),
+                                      torch.ones(self.T, dtype=torch.int32, device=dev))
+        # minibatches: contiguous document ranges with about the same number of tokens
+        bounds = [0]
+        for b in range(1, self.nbatch):
+            target = self.T * b // self.nbatch
+            bounds.append(int(torch.searchsorted(doc_ptr, torch.tensor([target], device=dev)).item()))
+        bounds.append(self.n_docs)
+        self.batches = []
+        max_vocab = 1
+        for b in range(self.nbatch):
+            d0, d1 = bounds[b], max(bounds[b + 1], bounds[b])
+            t0, t1 = int(doc_ptr[d0].item()), int(doc_ptr[d1].item())
+            vocab, widx = torch.unique(words[t0:t1], return_inverse=True)
+            self.batches.append({
+                "d0": d0, "d1": d1, "t0": t0, "t1": t1,
+                "ptr": (doc_ptr[d0:d1 + 1] - t0).contiguous(),
+                "vocab": vocab.contiguous(), "widx": widx.to(torch.int32).contiguous()})
+            max_vocab = max(max_vocab, vocab.numel())
+        self.cur = torch.zeros(max_vocab, K, dtype=torch.int32, device=dev)
+        self.old = torch.zeros(max_vocab, K, dtype=torch.int32, device=dev)
+        self.nk_cur = torch.zeros(1, K, dtype=torch.int32, device=dev)
+        self.nk_old = torch.zeros(1, K, dtype=torch.int32, device=dev)
+        # first push: this rank's initial counts
+        for bt in self.batches:
+            nv = bt["vocab"].numel()
+            if nv == 0:
+                continue
+            cnt = torch.zeros(nv, K, dtype=torch.int32, device=dev)
+            zz = self.z[bt["t0"]:bt["t1"]].long()
+            cnt.view(-1).index_add_(0, bt["widx"].long() * K + zz,
+                                    torch.ones(zz.numel(), dtype=torch.int32, device=dev))
+            self.wt.push(bt["vocab"], cnt)
+        nk = torch.bincount(self.z.long(), minlength=K).to(torch.int32).view(1, K).contiguous()
+        self.ts.push(self._zero_id, nk)
+        tot = torch.tensor([self.T], dtype=torch.int64, device=dev)
+        if self.world > 1:
+            dist.all_reduce(tot, group=self.group)
+        self.T_total = int(tot.item())
+        self._barrier()
+
+    def _barrier(self):
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    def step(self, with_loglik: bool = False):
+        bt = self.batches[self.step_no % self.nbatch]
+        it = self.step_no
+        self.step_no += 1
+        if self.world > 1:
+            self.clock.wait()
+        nv = bt["vocab"].numel()
+        nd = bt["d1"] - bt["d0"]
+        s = _lib.stream_ptr()
+        if nv > 0 and nd > 0:
+            cur, old = self.cur[:nv], self.old[:nv]
+            self.wt.pull(bt["vocab"], cur, old)
+            self.ts.pull(self._zero_id, self.nk_cur, self.nk_old)
+            _lib.call("pcl_lda_gibbs", bt["ptr"], bt["widx"], self.z[bt["t0"]:bt["t1"]],
+                      self.n_dk[bt["d0"]:bt["d1"]], cur, self.nk_cur, nd, self.K, self.alpha, self.beta,
+                      self.V * self.beta, (self.seed * 1000003 + it * 7919 + self.rank) & ((1 << 62) - 1),
+                      0, s)
+            if with_loglik:
+                _lib.call("pcl_lda_loglik", bt["ptr"], bt["widx"], self.n_dk[bt["d0"]:bt["d1"]], cur,
+                          self.nk_cur, self.doc_len[bt["d0"]:bt["d1"]], nd, self.K, self.alpha, self.beta,
+                          self.V * self.beta, self.ll, s)
+            self.wt.push(bt["vocab"], cur, old)
+            self.ts.push(self._zero_id, self.nk_cur, self.nk_old)
+        self.clock.commit()
+
+    def iteration(self, with_loglik: bool = False) -> Optional[float]:
+        """One pass over all local documents; optionally the global log-likelihood."""
+        if with_loglik:
+            self.ll.zero_()
+        for _ in range(self.nbatch):
+            self.step(with_loglik)
+        if with_loglik:
+            t = self.ll.clone()
+            if self.world > 1:
+                dist.all_reduce(t, group=self.group)
+            return float(t.item())
+        return None
+
+    def fit(self, with_loglik: bool = False) -> List[float]:
+        out = []
+        for _ in range(self.iters):
+            r = self.iteration(with_loglik)
+            if r is not None:
+                out.append(r)
+        self._barrier()
+        self.clock.check()
+        return out
+
+    def perplexity(self, loglik: float) -> float:
+        return math.exp(-loglik / max(self.T_total, 1))
+
+    def topic_word_counts(self) -> torch.Tensor:
+        """This rank's shard of the word-topic table (rows = owned word ids in owned_ids order)."""
+        return self.wt.shard
+
+    def free(self):
+        self._barrier()
+        for t in (self.wt, self.ts, self.clock):
+            t.free()

@@ -1,0 +1,131 @@
+"""PageRank with the rank vector sharded in HBM (device path of
+alg/graph_alg/pagerank/pr.hpp:40-200).
+
+Vertices are dense ids in [0, n); rank r owns the range ``[r*S, (r+1)*S)`` and keeps the
+in-links of its vertices as CSR.  What travels between ranks is the contribution vector
+``c(u) = pr(u) / outdeg(u)``: an iteration is ``read`` (all-gather of all shards by peer
+loads) and one pull kernel that evaluates ``pr(v) = (1 - d) + d * sum_{u->v} c(u)`` and writes
+the new contribution of every owned vertex straight into the owner's shard of the OTHER of
+two ping-pong tables (the reference's read_multi + write_multi, pr.hpp:140-168, without
+string keys).  Out-degrees are reduced through a ``DenseTable`` with the add handler.  An edge
+whose target is the sentinel 2147483648 only marks its source as a vertex with out-links."""
+from __future__ import annotations
+
+import os
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops.linear import pagerank_pull
+from ..ps.tables import DenseTable
+from ..utils.types import SENTINEL
+
+
+class PageRankGpu:
+    def __init__(self, n_vertices: int, damping: float = 0.85, group=None, device=None,
+                 threads_per_row: int = 8):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n, self.d = int(n_vertices), float(damping)
+        self.tables = [DenseTable(self.n, group, device, handler="add") for _ in range(2)]
+        self.device = self.tables[0].device
+        self.S = self.tables[0].S
+        self.lo, self.hi = self.tables[0].owned_range()
+        self.n_local = max(0, self.hi - self.lo)
+        self.tpr = threads_per_row
+        self.it = 0
+        self.delta_l1 = torch.zeros(1, dtype=torch.float64, device=self.device)
+
+    def owner_of(self, v: torch.Tensor) -> torch.Tensor:
+        return torch.clamp(v // self.S, max=self.world - 1)
+
+    def load_edges(self, src: torch.Tensor, dst: torch.Tensor):
+        """Edges whose destination this rank owns (plus sentinel edges of any source); the
+        out-degree of every vertex is summed over all ranks through the parameter table."""
+        dev = self.device
+        src = src.to(dev, torch.int64)
+        dst = dst.to(dev, torch.int64)
+        t = self.tables[0]
+        # out-degrees: reduce-scatter(add) of the local source counts
+        t.write(torch.zeros(self.n, device=dev))
+        t.delta().copy_(torch.bincount(src, minlength=self.n).to(torch.float32))
+        t.bupdate(handler="add")
+        outdeg_full = t.read().clone()
+        torch.cuda.synchronize(dev)
+        self._barrier()
+        real = dst != SENTINEL
+        src, dst = src[real], dst[real]
+        assert bool(((dst >= self.lo) & (dst < self.hi)).all()), "edges must be placed by destination owner"
+        order = torch.argsort(dst, stable=True)
+        self.cols = src[order].to(torch.int32).contiguous()
+        counts = torch.bincount(dst - self.lo, minlength=self.n_local)
+        self.row_ptr = torch.zeros(self.n_local + 1, dtype=torch.int64, device=dev)
+        self.row_ptr[1:] = torch.cumsum(counts, 0)
+        self.n_edges_local = int(self.cols.numel())
+        od = outdeg_full[self.lo:self.hi]
+        self.inv_outdeg = torch.where(od > 0, 1.0 / od.clamp(min=1.0), torch.zeros_like(od)).contiguous()
+        self.has_out = od > 0
+        N = int((outdeg_full[: self.n] > 0).sum().item())
+        self.N = N
+        init = 1.0 / max(N, 1)
+        self.rank_local = torch.where(self.has_out, torch.full_like(od, init), torch.zeros_like(od))
+        self.rank_new = torch.empty_like(self.rank_local)
+        # contribution table for iteration 0 lives in tables[0]
+        for tb in self.tables:
+            tb.shard.zero_()
+        self.tables[0].shard[: self.n_local] = self.rank_local * self.inv_outdeg
+        self.tables[0].mark_written()
+        self.it = 0
+
+    def _barrier(self):
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    def step(self, track_delta: bool = False):
+        cur, nxt = self.tables[self.it % 2], self.tables[(self.it + 1) % 2]
+        contrib = cur.read()
+        if track_delta:
+            self.delta_l1.zero_()
+        pagerank_pull(self.row_ptr, self.cols, contrib, self.inv_outdeg, self.d,
+                      nxt.shard, self.rank_new, self.delta_l1 if track_delta else None,
+                      self.rank_local if track_delta else None, self.tpr)
+        nxt.mark_written()
+        self.rank_local, self.rank_new = self.rank_new, self.rank_local
+        self.it += 1
+
+    def run(self, rounds: int):
+        for _ in range(rounds):
+            self.step()
+        self._barrier()
+        for t in self.tables:
+            t.check()
+
+    def ranks(self) -> torch.Tensor:
+        """Ranks of the owned vertices (vertices without out-links are reported as well)."""
+        return self.rank_local[: self.n_local]
+
+    def dump_result(self, outdir: str):
+        """``pagerank_0``: ``vertex\\trank`` for every vertex that has out-links (pr.hpp:184-193)."""
+        from ..utils.dump import dump_dict_scalar
+        os.makedirs(outdir, exist_ok=True)
+        self._barrier()
+        ids = (torch.nonzero(self.has_out).flatten() + self.lo).cpu().tolist()
+        vals = self.rank_local[self.has_out].cpu().tolist()
+        part = dict(zip(ids, vals))
+        parts = [part]
+        if self.world > 1:
+            parts = [None] * self.world
+            dist.all_gather_object(parts, part, group=self.group)
+        if self.rank == 0:
+            with open(os.path.join(outdir, "pagerank_0"), "w") as f:
+                for p in parts:
+                    dump_dict_scalar(p, f)
+        self._barrier()
+
+    def free(self):
+        self._barrier()
+        for t in self.tables:
+            t.free()

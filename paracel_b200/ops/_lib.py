@@ -52,6 +52,8 @@ SIGS = {
     "pcl_lr_dense_grad": "pppqiippppip",
     "pcl_lr_sparse_grad": "pppppqiippip",
     "pcl_pagerank_pull": "ppppqfppppip",
+    "pcl_lda_gibbs": "ppppppqifffQip",
+    "pcl_lda_loglik": "ppppppqifffpp",
     "pcl_ssp_commit": "piiqp",
     "pcl_ssp_wait": "piqQpip",
 }

@@ -185,6 +185,13 @@ class DenseTable:
                   self.lam if lam is None else float(lam), self.ready, self.epoch, self.timeout_ns,
                   self.status, self._done_table, self.counter, self.nnz if count_nnz else None, s)
 
+    def mark_written(self):
+        """The owner has rewritten its shard in place (e.g. a kernel stored new values there):
+        publish that as the next epoch so that readers wait for every owner."""
+        self.epoch += 1
+        _lib.call("pcl_publish_flag", self._done_table, self.world, self.rank, self.epoch,
+                  _lib.stream_ptr())
+
     def write(self, values: torch.Tensor):
         """Owner-side initialisation from a full vector that every rank passes identically."""
         lo, hi = self.owned_range()

@@ -287,3 +287,35 @@ def run_svd(comm, server_info, inp, out, k):
     m.dump_result()
     m.close()
     return {"sigma": m.sigma.tolist()}
+
+
+def checkpoint_resume(comm, server_info, inp, ckpt, phase):
+    """LR (dgd, deterministic) for 6 rounds at once, or 3 rounds + checkpoint, or resume + 3."""
+    import numpy as np
+    from paracel_b200.models.lr import logistic_regression
+    from paracel_b200.utils import checkpoint as C
+
+    class resumable(logistic_regression):
+        def _init_theta(self, dim):
+            if phase == "resume":
+                self.paracel_register_bupdate(self.update_file, self.update_func)
+                return
+            self.theta = np.full(dim, 0.5)
+            self.paracel_write("theta", self.theta.tolist())
+            self.paracel_register_bupdate(self.update_file, self.update_func)
+
+    rounds = 6 if phase == "full" else 3
+    m = resumable(comm, server_info, inp, "", method="dgd", rounds=rounds, alpha=1e-4, beta=0.0, seed=1)
+    if phase == "resume":
+        C.load_servers(m, ckpt)
+        meta = C.load_meta(ckpt)
+        assert meta["rounds_done"] == 3 and meta["world"] == comm.get_size()
+    m.solve()
+    if phase == "first":
+        C.save_servers(m, ckpt)
+        if comm.get_rank() == 0:
+            C.save_meta(ckpt, {"rounds_done": 3, "world": comm.get_size()})
+        C.save_rank_state(ckpt, comm.get_rank(), {"theta": m.theta, "rank": comm.get_rank()})
+    theta = m.theta.tolist()
+    m.close()
+    return theta

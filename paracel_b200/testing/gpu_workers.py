@@ -200,3 +200,57 @@ def dense_table_two_ranks(comm, server_info):
     comm.synchronize()
     t.free()
     return ok
+
+
+def l1lr_and_pagerank_two_ranks(comm, server_info):
+    """Sparse L1-LR and PageRank on 2 ranks give what 1 rank gives on the union of the data."""
+    from paracel_b200.models.linear_gpu import SparseLinearGpu
+    from paracel_b200.models.pagerank_gpu import PageRankGpu
+    rank, world = comm.get_rank(), comm.get_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev)
+    g.manual_seed(21)
+    n, F, k = 8000, 2048, 10
+    cols = (torch.rand(n, k, device=dev, generator=g) ** 2 * F).long().clamp(max=F - 1)
+    y = (torch.rand(n, device=dev, generator=g) < 0.5).float()
+    lo, hi = rank * n // world, (rank + 1) * n // world
+    m = SparseLinearGpu(F, eta=1.0, lam=1e-3, nbatch=1, hot_T=512)
+    m.load(torch.arange(0, (hi - lo) * k + 1, k, device=dev, dtype=torch.int64),
+           cols[lo:hi].reshape(-1).int().contiguous(), y[lo:hi])
+    for _ in range(10):
+        m.step()
+    w = m.weights()
+    torch.cuda.synchronize()
+    m.table.check()
+    th = torch.zeros(F, device=dev, dtype=torch.float64)
+    for _ in range(10):
+        r = y.double() - torch.sigmoid(th[cols].sum(1))
+        gg = torch.zeros(F, device=dev, dtype=torch.float64)
+        gg.index_add_(0, cols.reshape(-1), r[:, None].expand(-1, k).reshape(-1))
+        wv = th + gg / n
+        th = torch.sign(wv) * torch.clamp(wv.abs() - 1e-3 / n, min=0)
+    ok_lr = bool(torch.allclose(w.double(), th, rtol=2e-3, atol=2e-4))
+    comm.synchronize()
+    m.free()
+    # PageRank
+    nv, ne = 4001, 50000
+    g.manual_seed(22)
+    src = torch.randint(0, nv, (ne,), device=dev, generator=g)
+    dst = (torch.rand(ne, device=dev, generator=g) ** 2 * nv).long().clamp(max=nv - 1)
+    pr = PageRankGpu(nv, 0.85)
+    mine = pr.owner_of(dst) == rank
+    pr.load_edges(src[mine], dst[mine])
+    pr.run(12)
+    outdeg = torch.bincount(src, minlength=nv).double()
+    has = outdeg > 0
+    ref = torch.where(has, torch.full((nv,), 1.0 / int(has.sum()), device=dev, dtype=torch.float64),
+                      torch.zeros(nv, device=dev, dtype=torch.float64))
+    for _ in range(12):
+        c = torch.where(has, ref / outdeg.clamp(min=1), torch.zeros_like(ref))
+        acc = torch.zeros(nv, device=dev, dtype=torch.float64)
+        acc.index_add_(0, dst, c[src])
+        ref = 0.15 + 0.85 * acc
+    ok_pr = bool(torch.allclose(pr.ranks().double(), ref[pr.lo:pr.hi], rtol=1e-4, atol=1e-6))
+    comm.synchronize()
+    pr.free()
+    return ok_lr, ok_pr

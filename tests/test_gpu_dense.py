@@ -117,3 +117,102 @@ def test_pagerank_pull_matches_dense_reference():
         torch.testing.assert_close(newr.double(), ref, rtol=1e-5, atol=1e-6)
         torch.testing.assert_close(newc, newr * inv, rtol=1e-6, atol=1e-8)
         assert abs(float(dl.item()) - float((ref - pr.double()).abs().sum())) < 1e-3
+
+
+def _sparse_problem(dev, n=20000, F=4096, nnz_row=12, seed=0):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    cols = (torch.rand(n, nnz_row, device=dev, generator=g) ** 2 * F).long().clamp(max=F - 1)
+    w = torch.zeros(F, device=dev)
+    idx = torch.randperm(F, device=dev, generator=g)[: F // 50]
+    w[idx] = 2.0 * torch.randn(idx.numel(), device=dev, generator=g)
+    z = w[cols].sum(1)
+    y = (torch.rand(n, device=dev, generator=g) < torch.sigmoid(z)).float()
+    row_ptr = torch.arange(0, n * nnz_row + 1, nnz_row, device=dev, dtype=torch.int64)
+    return row_ptr, cols.view(-1).int().contiguous(), y, w
+
+
+def test_sparse_l1_logistic_regression_single_gpu():
+    from paracel_b200.models.linear_gpu import SparseLinearGpu, remap_by_frequency
+    dev = "cuda:0"
+    row_ptr, cols, y, w_true = _sparse_problem(dev)
+    F = w_true.numel()
+    cols2, order = remap_by_frequency(cols, F)
+    m = SparseLinearGpu(F, eta=2.0, lam=2e-4, nbatch=4, device=dev, hot_T=1024)
+    m.load(row_ptr, cols2, y)
+    losses = []
+    for ep in range(30):
+        m.epoch()
+        losses.append(m.mean_loss())
+    torch.cuda.synchronize()
+    m.table.check()
+    w = m.weights()
+    # oracle: the same proximal-gradient iteration in fp64 with plain torch ops
+    th = torch.zeros(F, device=dev, dtype=torch.float64)
+    n = y.numel()
+    C = cols2.long().view(n, -1)
+    b = torch.linspace(0, n, 5).long().tolist()
+    for ep in range(30):
+        for k in range(4):
+            lo, hi = b[k], b[k + 1]
+            z = th[C[lo:hi]].sum(1)
+            r = y[lo:hi].double() - torch.sigmoid(z)
+            g = torch.zeros(F, device=dev, dtype=torch.float64)
+            g.index_add_(0, C[lo:hi].reshape(-1), r[:, None].expand(-1, C.shape[1]).reshape(-1))
+            wv = th + (2.0 / (n / 4)) * g
+            t = (2.0 / (n / 4)) * 2e-4
+            th = torch.sign(wv) * torch.clamp(wv.abs() - t, min=0)
+    torch.testing.assert_close(w.double(), th, rtol=2e-3, atol=2e-4)
+    assert losses[-1] < losses[0]
+    assert m.nnz_weights() == int((w != 0).sum().item()) < F
+    m.free()
+
+
+def test_dense_logistic_regression_single_gpu():
+    from paracel_b200.models.linear_gpu import DenseLinearGpu
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(4)
+    n, d = 20000, 101
+    X = torch.randn(n, d, device=dev, generator=g)
+    X[:, 0] = 1.0
+    w = torch.randn(d, device=dev, generator=g)
+    y = (torch.rand(n, device=dev, generator=g) < torch.sigmoid(X @ w)).float()
+    m = DenseLinearGpu(d, eta=1.0, device=dev)
+    m.load(X, y)
+    th = torch.zeros(d, device=dev, dtype=torch.float64)
+    for it in range(40):
+        m.step()
+        h = torch.sigmoid(X.double() @ th)
+        th = th + (1.0 / n) * (X.double().T @ (y.double() - h))
+    torch.testing.assert_close(m.weights().double(), th, rtol=1e-3, atol=1e-4)
+    assert m.mean_loss() < 0.45
+    m.free()
+
+
+def test_pagerank_gpu_matches_power_iteration():
+    from paracel_b200.models.pagerank_gpu import PageRankGpu
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(6)
+    n, m_edges = 5000, 60000
+    src = torch.randint(0, n, (m_edges,), device=dev, generator=g)
+    dst = (torch.rand(m_edges, device=dev, generator=g) ** 2 * n).long().clamp(max=n - 1)
+    # one vertex that only has the "no out-link" marker
+    src = torch.cat([src, torch.tensor([n - 1], device=dev)])
+    dst = torch.cat([dst, torch.tensor([2147483648], device=dev)])
+    pr = PageRankGpu(n, 0.85, device=dev)
+    pr.load_edges(src, dst)
+    pr.run(15)
+    got = pr.ranks().double()
+    outdeg = torch.bincount(src, minlength=n).double()
+    has = outdeg > 0
+    ref = torch.where(has, torch.full((n,), 1.0 / int(has.sum()), device=dev, dtype=torch.float64), torch.zeros(n, device=dev, dtype=torch.float64))
+    real = dst != 2147483648
+    s, d_ = src[real], dst[real]
+    for _ in range(15):
+        c = torch.where(has, ref / outdeg.clamp(min=1), torch.zeros_like(ref))
+        acc = torch.zeros(n, device=dev, dtype=torch.float64)
+        acc.index_add_(0, d_, c[s])
+        ref = 0.15 + 0.85 * acc
+    torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-6)
+    pr.step(track_delta=True)
+    assert float(pr.delta_l1.item()) >= 0.0
+    pr.free()

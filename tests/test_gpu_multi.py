@@ -64,3 +64,10 @@ def test_fused_allgather_gemm_two_ranks():
 def test_dense_table_reduce_scatter_handler_two_ranks():
     from paracel_b200.testing.gpu_workers import dense_table_two_ranks
     assert all(_job(2).run(dense_table_two_ranks, timeout_s=300))
+
+
+@needs2
+def test_sparse_l1lr_and_pagerank_two_ranks():
+    from paracel_b200.testing.gpu_workers import l1lr_and_pagerank_two_ranks
+    for ok_lr, ok_pr in _job(2).run(l1lr_and_pagerank_two_ranks, timeout_s=300):
+        assert ok_lr and ok_pr
