@@ -1,0 +1,174 @@
+// Batched ALS normal equations: for every user u with rated items I_u and ratings a_u,
+//   w_u = (H_u^T H_u + lambda I)^-1 H_u^T a_u
+// (reference: alg/recommendation/als/als.hpp:133-165, which forms the k x k matrix with Eigen
+// and multiplies by its explicit inverse).  Here one CTA of 256 threads handles one work
+// item = one segment of a user's ratings: the 16 x 16 thread grid keeps the k x k Gram
+// matrix in registers ((k/16)^2 per thread), item rows are staged through shared memory 8 at
+// a time, and the system is solved in shared memory by Cholesky factorisation and two
+// triangular solves.  Users with more ratings than one segment holds are split: every
+// segment adds its partial Gram matrix and right-hand side into a scratch slot with atomics
+// and the segment that arrives last solves.
+#include "common.cuh"
+
+namespace {
+
+struct AlsArgs {
+  const int* seg_user;         // n_seg: user index of the segment
+  const long long* seg_begin;  // n_seg: first rating (index into item_idx / rating)
+  const long long* seg_end;    // n_seg
+  const int* user_nseg;        // n_users: number of segments of the user
+  const int* user_slot;        // n_users: scratch slot for split users, -1 otherwise
+  const int* item_idx;         // nnz: row of H
+  const float* rating;         // nnz
+  const float* H;              // n_items x k
+  float* W;                    // n_users x k (output)
+  float* scratch;              // n_slots x (k*k + k), zero-initialised
+  unsigned int* slot_count;    // n_slots, zero-initialised
+  long long n_seg;
+  int k;
+  float lambda;
+};
+
+template <int KB>
+__global__ void __launch_bounds__(256) als_kernel(AlsArgs a) {
+  constexpr int K = 16 * KB;
+  extern __shared__ float sm[];
+  float* sA = sm;                       // K x (K + 1)
+  float* sb = sA + K * (K + 1);         // K
+  float* sh = sb + K;                   // 8 x K staged item rows
+  float* sr = sh + 8 * K;               // 8 ratings
+  __shared__ int s_last;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  for (long long seg = blockIdx.x; seg < a.n_seg; seg += gridDim.x) {
+    const int u = a.seg_user[seg];
+    const long long b0 = a.seg_begin[seg], b1 = a.seg_end[seg];
+    float acc[KB][KB];
+#pragma unroll
+    for (int i = 0; i < KB; ++i)
+#pragma unroll
+      for (int j = 0; j < KB; ++j) acc[i][j] = 0.f;
+    float bacc = 0.f;  // threads 0..K-1 own one entry of H^T a
+    for (long long p = b0; p < b1; p += 8) {
+      const int cnt = (int)((b1 - p) < 8 ? (b1 - p) : 8);
+      __syncthreads();
+      for (int e = tid; e < cnt * K; e += 256) {
+        const int r = e / K, c = e % K;
+        sh[r * K + c] = (c < a.k) ? __ldg(a.H + (long long)a.item_idx[p + r] * a.k + c) : 0.f;
+      }
+      if (tid < cnt) sr[tid] = a.rating[p + tid];
+      __syncthreads();
+      for (int r = 0; r < cnt; ++r) {
+        float hy[KB], hx[KB];
+#pragma unroll
+        for (int i = 0; i < KB; ++i) { hy[i] = sh[r * K + ty * KB + i]; hx[i] = sh[r * K + tx * KB + i]; }
+#pragma unroll
+        for (int i = 0; i < KB; ++i)
+#pragma unroll
+          for (int j = 0; j < KB; ++j) acc[i][j] = fmaf(hy[i], hx[j], acc[i][j]);
+        if (tid < K) bacc = fmaf(sr[r], sh[r * K + tid], bacc);
+      }
+    }
+    const int slot = a.user_slot[u];
+    bool solve_here = true;
+    if (slot >= 0) {
+      // split user: add the partial sums, the last segment to arrive solves
+      float* gA = a.scratch + (long long)slot * (K * K + K);
+#pragma unroll
+      for (int i = 0; i < KB; ++i)
+#pragma unroll
+        for (int j = 0; j < KB; ++j) atomicAdd(gA + (ty * KB + i) * K + tx * KB + j, acc[i][j]);
+      if (tid < K) atomicAdd(gA + K * K + tid, bacc);
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        const unsigned int prev = atomicAdd(a.slot_count + slot, 1u);
+        s_last = (prev == (unsigned int)a.user_nseg[u] - 1) ? 1 : 0;
+      }
+      __syncthreads();
+      solve_here = (s_last != 0);
+      if (solve_here) {
+        __threadfence();
+#pragma unroll
+        for (int i = 0; i < KB; ++i)
+#pragma unroll
+          for (int j = 0; j < KB; ++j) acc[i][j] = __ldcg(gA + (ty * KB + i) * K + tx * KB + j);
+        if (tid < K) bacc = __ldcg(gA + K * K + tid);
+      }
+    }
+    if (!solve_here) continue;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < KB; ++i)
+#pragma unroll
+      for (int j = 0; j < KB; ++j) {
+        const int r = ty * KB + i, c = tx * KB + j;
+        sA[r * (K + 1) + c] = acc[i][j] + (r == c ? a.lambda : 0.f);
+      }
+    if (tid < K) sb[tid] = bacc;
+    __syncthreads();
+    // Cholesky A = L L^T in place (lower triangle)
+    for (int j = 0; j < K; ++j) {
+      if (tid == 0) sA[j * (K + 1) + j] = sqrtf(fmaxf(sA[j * (K + 1) + j], 1e-30f));
+      __syncthreads();
+      const float inv = 1.f / sA[j * (K + 1) + j];
+      for (int i = j + 1 + tid; i < K; i += 256) sA[i * (K + 1) + j] *= inv;
+      __syncthreads();
+      const int m = K - j - 1;
+      for (int e = tid; e < m * m; e += 256) {
+        const int r = j + 1 + e / m, c = j + 1 + e % m;
+        if (c <= r) sA[r * (K + 1) + c] -= sA[r * (K + 1) + j] * sA[c * (K + 1) + j];
+      }
+      __syncthreads();
+    }
+    // forward: L y = b
+    for (int j = 0; j < K; ++j) {
+      if (tid == 0) sb[j] /= sA[j * (K + 1) + j];
+      __syncthreads();
+      const float yj = sb[j];
+      for (int i = j + 1 + tid; i < K; i += 256) sb[i] -= sA[i * (K + 1) + j] * yj;
+      __syncthreads();
+    }
+    // backward: L^T w = y
+    for (int j = K - 1; j >= 0; --j) {
+      if (tid == 0) sb[j] /= sA[j * (K + 1) + j];
+      __syncthreads();
+      const float wj = sb[j];
+      for (int i = tid; i < j; i += 256) sb[i] -= sA[j * (K + 1) + i] * wj;
+      __syncthreads();
+    }
+    if (tid < a.k) a.W[(long long)u * a.k + tid] = sb[tid];
+    __syncthreads();
+  }
+}
+
+template <int KB>
+int launch(const AlsArgs& a, int blocks, cudaStream_t stream) {
+  constexpr int K = 16 * KB;
+  size_t smem = (size_t)(K * (K + 1) + K + 8 * K + 8) * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(als_kernel<KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  als_kernel<KB><<<blocks, 256, smem, stream>>>(a);
+  return pcl_last_error();
+}
+
+}  // namespace
+
+// k <= 128.  Work items are segments (seg_user, [seg_begin, seg_end)); a user with more than
+// one segment needs user_slot[u] >= 0 and zeroed `scratch` (slots x (K*K + K) floats, K = k
+// rounded up to 32/64/96/128) and `slot_count`.
+PCL_API int pcl_als_solve(const int* seg_user, const long long* seg_begin, const long long* seg_end,
+                          const int* user_nseg, const int* user_slot, const int* item_idx,
+                          const float* rating, const float* H, float* W, float* scratch,
+                          unsigned int* slot_count, long long n_seg, int k, float lambda, int blocks,
+                          cudaStream_t stream) {
+  if (n_seg <= 0) return 0;
+  if (k <= 0 || k > 128) return (int)cudaErrorInvalidValue;
+  AlsArgs a{seg_user, seg_begin, seg_end, user_nseg, user_slot, item_idx, rating, H, W, scratch,
+            slot_count, n_seg, k, lambda};
+  if (blocks <= 0) blocks = 148 * 2;
+  if (n_seg < blocks) blocks = (int)n_seg;
+  if (k <= 32) return launch<2>(a, blocks, stream);
+  if (k <= 64) return launch<4>(a, blocks, stream);
+  if (k <= 96) return launch<6>(a, blocks, stream);
+  return launch<8>(a, blocks, stream);
+}

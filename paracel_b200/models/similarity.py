@@ -69,19 +69,24 @@ class sim_dense(paralg):
         if self.device:
             import torch
             from ..ops.gemm import gemm_nt
+            from ..ops.misc import RunningTopK
             Xa = torch.tensor(self.X, dtype=torch.float32, device="cuda")
+            topk = RunningTopK(torch.tensor(self.ids, device="cuda"), self.ktop, self.simbar)
 
         def handler(lines):
             ids_b, B = self._parse(lines)
             if B.shape[0] == 0 or self.X.shape[0] == 0:
                 return
             if self.device:
+                # GEMM tile on the tensor cores (3xTF32), top-k merge on the GPU
                 Bt = torch.tensor(B, dtype=torch.float32, device="cuda")
-                S = gemm_nt(Xa, Bt, precise=True).double().cpu().numpy()
-            else:
-                S = self.X @ B.T
-            self._merge(self.ids, ids_b, S)
+                topk.update(gemm_nt(Xa, Bt, precise=True), torch.tensor(ids_b, device="cuda"))
+                return
+            self._merge(self.ids, ids_b, self.X @ B.T)
         self.paracel_sequential_loadall(self.input_b, handler)
+        if self.device:
+            self.result = topk.result() if self.X.shape[0] else {}
+            return
         self.result = {i: [(j, s) for s, j in sorted(h, reverse=True)] for i, h in self.heaps.items()}
 
     def dump_result(self):

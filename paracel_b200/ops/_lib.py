@@ -54,6 +54,11 @@ SIGS = {
     "pcl_pagerank_pull": "ppppqfppppip",
     "pcl_lda_gibbs": "ppppppqifffQip",
     "pcl_lda_loglik": "ppppppqifffpp",
+    "pcl_als_solve": "pppppppppppqifip",
+    "pcl_kmeans_accumulate": "ppqippp",
+    "pcl_topk_rows": "pqiippfippp",
+    "pcl_gram": "pqipp",
+    "pcl_allreduce_sum_f64": "ppipppiiiqQpp",
     "pcl_ssp_commit": "piiqp",
     "pcl_ssp_wait": "piqQpip",
 }

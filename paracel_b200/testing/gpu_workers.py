@@ -254,3 +254,74 @@ def l1lr_and_pagerank_two_ranks(comm, server_info):
     comm.synchronize()
     pr.free()
     return ok_lr, ok_pr
+
+
+def kmeans_allreduce_lda_two_ranks(comm, server_info):
+    """k-means (fused gather + arg-min GEMM, reduce-scatter of the sums), the one-launch
+    all-reduce and the LDA sampler with sparse pulls / pushes on 2 ranks."""
+    import numpy as np
+    from paracel_b200.models.kmeans_gpu import KMeansGpu
+    from paracel_b200.models.lda_gpu import LdaGibbsGpu
+    from paracel_b200.ops.misc import DeviceAllReduce
+    rank, world = comm.get_rank(), comm.get_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = {}
+    ar = DeviceAllReduce()
+    ok = True
+    for it in range(4):
+        x = torch.arange(6, dtype=torch.float64, device=dev) * (rank + 1) + it
+        y = ar(x)
+        torch.cuda.synchronize()
+        exp = torch.arange(6, dtype=torch.float64, device=dev) * sum(r + 1 for r in range(world)) + it * world
+        ok = ok and bool(torch.equal(y, exp))
+    ar.check()
+    out["allreduce"] = ok
+    comm.synchronize()
+    ar.free()
+    # k-means: the same data split over the ranks must give the single-process Lloyd result
+    g = torch.Generator(device=dev)
+    g.manual_seed(31)
+    k, d, n = 12, 6, 4000
+    C0 = 5 * torch.randn(k, d, device=dev, generator=g)
+    lab = torch.randint(0, k, (n,), device=dev, generator=g)
+    X = C0[lab] + 0.4 * torch.randn(n, d, device=dev, generator=g)
+    lo, hi = rank * n // world, (rank + 1) * n // world
+    m = KMeansGpu(k, d)
+    m.load(X[lo:hi], init_centres=X[:k].clone())
+    m.fit(5)
+    C = m.cluster_centres().double().cpu().numpy()
+    Xn = X.double().cpu().numpy()
+    Cr = Xn[:k].copy()
+    for _ in range(5):
+        a = ((Cr * Cr).sum(1)[None, :] - 2 * Xn @ Cr.T).argmin(1)
+        for c in range(k):
+            if (a == c).any():
+                Cr[c] = Xn[a == c].mean(0)
+    out["kmeans"] = bool(np.allclose(C, Cr, rtol=1e-3, atol=1e-3))
+    comm.synchronize()
+    m.free()
+    # LDA: global bookkeeping stays exact with SSP staleness 2 and sparse pulls / pushes
+    rng = np.random.default_rng(5)
+    V, K, ndocs = 300, 128, 200
+    ptr, words = [0], []
+    for dd in range(ndocs):
+        nn = int(rng.integers(20, 60))
+        words.extend(rng.integers(0, V, nn).tolist())
+        ptr.append(len(words))
+    ptr, words = np.asarray(ptr), np.asarray(words)
+    d0, d1 = rank * ndocs // world, (rank + 1) * ndocs // world
+    lda = LdaGibbsGpu(V, K, iters=5, nbatch=3, staleness=2, seed=2)
+    lda.load_docs(torch.tensor(ptr[d0:d1 + 1] - ptr[d0]), torch.tensor(words[ptr[d0]:ptr[d1]]))
+    ll = lda.fit(with_loglik=True)
+    tot = torch.tensor([int(lda.wt.shard.sum().item()), int(lda.ts.shard.sum().item())], device=dev)
+    dist.all_reduce(tot)
+    out["lda_counts"] = (int(tot[0]), int(tot[1]), len(words))
+    out["lda_ll_up"] = ll[-1] > ll[0]
+    colsum = lda.wt.shard.sum(0).clone()
+    dist.all_reduce(colsum)
+    nk = lda.ts.shard[0].clone() if rank == 0 else torch.zeros_like(lda.ts.shard[0])
+    dist.all_reduce(nk)
+    out["lda_consistent"] = bool(torch.equal(colsum.int(), nk.int()))
+    comm.synchronize()
+    lda.free()
+    return out

@@ -1,0 +1,96 @@
+"""Batched ALS solve, k-means, top-k merge, Gram and the one-launch all-reduce on one GPU."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("k", [8, 32, 50, 128])
+def test_als_batched_solve_matches_numpy(k):
+    from paracel_b200.ops.als import als_solve
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(k)
+    ni, nu = 500, 300
+    H = torch.randn(ni, k, device=dev, generator=g)
+    cnt = torch.randint(1, 40, (nu,), device=dev, generator=g)
+    cnt[0] = 0                      # a user without ratings keeps a zero factor
+    cnt[5] = 9000                   # a heavy user is split over several CTAs
+    ptr = torch.zeros(nu + 1, dtype=torch.int64, device=dev)
+    ptr[1:] = torch.cumsum(cnt, 0)
+    nnz = int(ptr[-1])
+    idx = torch.randint(0, ni, (nnz,), device=dev, generator=g).int()
+    r = torch.randn(nnz, device=dev, generator=g)
+    lam = 0.5
+    W = als_solve(ptr, idx, r, H, lam, seg_len=1024)
+    torch.cuda.synchronize()
+    Hn, pn, idn, rn = H.double().cpu().numpy(), ptr.cpu().numpy(), idx.cpu().numpy(), r.double().cpu().numpy()
+    for u in (0, 1, 5, 77, 299):
+        Hs = Hn[idn[pn[u]:pn[u + 1]]]
+        if Hs.shape[0] == 0:
+            assert float(W[u].abs().sum()) == 0.0
+            continue
+        ref = np.linalg.solve(Hs.T @ Hs + lam * np.eye(k), Hs.T @ rn[pn[u]:pn[u + 1]])
+        assert np.allclose(W[u].cpu().numpy(), ref, rtol=2e-3, atol=2e-4), u
+
+
+def test_kmeans_gpu_matches_numpy_lloyd():
+    from paracel_b200.models.kmeans_gpu import KMeansGpu
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(7)
+    k, d, n = 16, 10, 6000
+    C0 = 6 * torch.randn(k, d, device=dev, generator=g)
+    lab = torch.randint(0, k, (n,), device=dev, generator=g)
+    X = C0[lab] + 0.5 * torch.randn(n, d, device=dev, generator=g)
+    m = KMeansGpu(k, d, device=dev)
+    m.load(X)
+    m.fit(6)
+    C = m.cluster_centres().double().cpu().numpy()
+    Xn = X.double().cpu().numpy()
+    Cr = Xn[:k].copy()
+    for _ in range(6):
+        a = ((Cr * Cr).sum(1)[None, :] - 2 * Xn @ Cr.T).argmin(1)
+        for c in range(k):
+            if (a == c).any():
+                Cr[c] = Xn[a == c].mean(0)
+    assert np.allclose(C, Cr, rtol=1e-3, atol=1e-3)
+    m.free()
+
+
+def test_running_topk_and_gram():
+    from paracel_b200.ops.misc import RunningTopK, gram
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(9)
+    m, n, k = 300, 1000, 7
+    S = torch.randn(m, n, device=dev, generator=g)
+    row_ids = torch.arange(m, device=dev) * 3
+    col_ids = torch.arange(n, device=dev)
+    tk = RunningTopK(row_ids, k, lower=0.5)
+    for c0 in range(0, n, 256):           # tiles arrive one after the other
+        tk.update(S[:, c0:c0 + 256].contiguous(), col_ids[c0:c0 + 256])
+    torch.cuda.synchronize()
+    res = tk.result()
+    Sm = S.clone()
+    Sm[row_ids[:, None] == col_ids[None, :]] = -1e30   # self excluded
+    for r in (0, 1, 150, 299):
+        vals, idx = torch.topk(Sm[r], k)
+        exp = [(int(i), float(v)) for v, i in zip(vals, idx) if v >= 0.5]
+        got = res.get(int(row_ids[r]), [])
+        assert [i for i, _ in got] == [i for i, _ in exp]
+        assert np.allclose([v for _, v in got], [v for _, v in exp])
+    H = torch.randn(5000, 50, device=dev, generator=g)
+    G = gram(H)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(G.double(), H.double().T @ H.double(), rtol=1e-4, atol=1e-2)
+
+
+def test_device_allreduce_single_rank():
+    from paracel_b200.ops.misc import DeviceAllReduce
+    ar = DeviceAllReduce(device="cuda:0")
+    x = torch.arange(10, dtype=torch.float64, device="cuda:0")
+    for _ in range(3):
+        y = ar(x)
+    torch.cuda.synchronize()
+    ar.check()
+    assert torch.equal(x, y)
+    ar.free()

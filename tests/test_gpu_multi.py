@@ -71,3 +71,12 @@ def test_sparse_l1lr_and_pagerank_two_ranks():
     from paracel_b200.testing.gpu_workers import l1lr_and_pagerank_two_ranks
     for ok_lr, ok_pr in _job(2).run(l1lr_and_pagerank_two_ranks, timeout_s=300):
         assert ok_lr and ok_pr
+
+
+@needs2
+def test_kmeans_allreduce_lda_two_ranks():
+    from paracel_b200.testing.gpu_workers import kmeans_allreduce_lda_two_ranks
+    for r in _job(2).run(kmeans_allreduce_lda_two_ranks, timeout_s=300):
+        assert r["allreduce"] and r["kmeans"], r
+        assert r["lda_counts"][0] == r["lda_counts"][2] == r["lda_counts"][1], r
+        assert r["lda_ll_up"] and r["lda_consistent"], r
