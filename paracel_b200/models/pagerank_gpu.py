@@ -17,14 +17,14 @@ from typing import Dict, Optional
 import torch
 import torch.distributed as dist
 
-from ..ops.linear import pagerank_pull
+from ..ops.linear import pagerank_pull, pagerank_pull_stream, pagerank_stream_plan
 from ..ps.tables import DenseTable
 from ..utils.types import SENTINEL
 
 
 class PageRankGpu:
     def __init__(self, n_vertices: int, damping: float = 0.85, group=None, device=None,
-                 threads_per_row: int = 8):
+                 threads_per_row: int = 8, edge_balanced: bool = True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -35,6 +35,7 @@ class PageRankGpu:
         self.lo, self.hi = self.tables[0].owned_range()
         self.n_local = max(0, self.hi - self.lo)
         self.tpr = threads_per_row
+        self.edge_balanced = edge_balanced
         self.it = 0
         self.delta_l1 = torch.zeros(1, dtype=torch.float64, device=self.device)
 
@@ -64,6 +65,8 @@ class PageRankGpu:
         self.row_ptr = torch.zeros(self.n_local + 1, dtype=torch.int64, device=dev)
         self.row_ptr[1:] = torch.cumsum(counts, 0)
         self.n_edges_local = int(self.cols.numel())
+        self.heavy_deg = 2048
+        self.heavy_rows = torch.nonzero(counts > self.heavy_deg).flatten().to(torch.int32).contiguous()
         od = outdeg_full[self.lo:self.hi]
         self.inv_outdeg = torch.where(od > 0, 1.0 / od.clamp(min=1.0), torch.zeros_like(od)).contiguous()
         self.has_out = od > 0
@@ -72,6 +75,8 @@ class PageRankGpu:
         init = 1.0 / max(N, 1)
         self.rank_local = torch.where(self.has_out, torch.full_like(od, init), torch.zeros_like(od))
         self.rank_new = torch.empty_like(self.rank_local)
+        self.acc = torch.zeros(max(self.n_local, 1), device=dev)
+        self.plan = pagerank_stream_plan(self.row_ptr)
         # contribution table for iteration 0 lives in tables[0]
         for tb in self.tables:
             tb.shard.zero_()
@@ -89,9 +94,15 @@ class PageRankGpu:
         contrib = cur.read()
         if track_delta:
             self.delta_l1.zero_()
-        pagerank_pull(self.row_ptr, self.cols, contrib, self.inv_outdeg, self.d,
-                      nxt.shard, self.rank_new, self.delta_l1 if track_delta else None,
-                      self.rank_local if track_delta else None, self.tpr)
+        if self.edge_balanced:
+            pagerank_pull_stream(self.row_ptr, self.cols, contrib, self.inv_outdeg, self.d, self.acc,
+                                 nxt.shard, self.rank_new, self.delta_l1 if track_delta else None,
+                                 self.rank_local if track_delta else None, self.plan)
+        else:
+            pagerank_pull(self.row_ptr, self.cols, contrib, self.inv_outdeg, self.d,
+                          nxt.shard, self.rank_new, self.delta_l1 if track_delta else None,
+                          self.rank_local if track_delta else None, self.tpr,
+                          self.heavy_rows if self.heavy_rows.numel() else None, self.heavy_deg)
         nxt.mark_written()
         self.rank_local, self.rank_new = self.rank_new, self.rank_local
         self.it += 1

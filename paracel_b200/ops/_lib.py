@@ -51,7 +51,8 @@ SIGS = {
     "pcl_publish_flag": "piiqp",
     "pcl_lr_dense_grad": "pppqiippppip",
     "pcl_lr_sparse_grad": "pppppqiippip",
-    "pcl_pagerank_pull": "ppppqfppppip",
+    "pcl_pagerank_pull": "ppppqfppppiqpip",
+    "pcl_pagerank_pull_stream": "ppppqqppfpppppp",
     "pcl_lda_gibbs": "ppppppqifffQip",
     "pcl_lda_loglik": "ppppppqifffpp",
     "pcl_als_solve": "pppppppppppqifip",

@@ -36,7 +36,43 @@ def sparse_grad(row_ptr, cols, vals, y, theta, g, loss, logistic: bool = True, h
 
 
 def pagerank_pull(row_ptr, cols, contrib, inv_outdeg, damping, new_contrib, new_rank=None,
-                  delta_l1=None, old_rank=None, threads_per_row: int = 8):
+                  delta_l1=None, old_rank=None, threads_per_row: int = 8, heavy_rows=None,
+                  heavy_deg: int = 2048):
+    """``heavy_rows`` (int32 list of rows with more than ``heavy_deg`` in-links) are reduced by a
+    whole thread block each instead of ``threads_per_row`` threads."""
     n = row_ptr.numel() - 1
+    nh = 0 if heavy_rows is None else heavy_rows.numel()
     _lib.call("pcl_pagerank_pull", row_ptr, cols, contrib, inv_outdeg, n, float(damping), new_contrib,
-              new_rank, delta_l1, old_rank, threads_per_row, _lib.stream_ptr())
+              new_rank, delta_l1, old_rank, threads_per_row, int(heavy_deg), heavy_rows, nh,
+              _lib.stream_ptr())
+
+
+PR_CAP = 2048
+
+
+def pagerank_stream_plan(row_ptr):
+    """Static per-graph plan of the edge-balanced kernel: for every block of 2048 in-links the row
+    that holds its first and the row that holds its last in-link (int32 arrays)."""
+    nnz = int(row_ptr[-1].item())
+    nb = (nnz + PR_CAP - 1) // PR_CAP
+    if nb == 0:
+        z = row_ptr.new_zeros(0, dtype=torch.int32)
+        return z, z
+    starts = torch.arange(nb, device=row_ptr.device, dtype=torch.int64) * PR_CAP
+    lasts = torch.clamp(starts + PR_CAP, max=nnz) - 1
+    first = torch.searchsorted(row_ptr, starts, right=True) - 1
+    last = torch.searchsorted(row_ptr, lasts, right=True) - 1
+    return first.to(torch.int32).contiguous(), last.to(torch.int32).contiguous()
+
+
+def pagerank_pull_stream(row_ptr, cols, contrib, inv_outdeg, damping, acc, new_contrib, new_rank=None,
+                         delta_l1=None, old_rank=None, plan=None):
+    """Edge-balanced pull step: blocks own equal numbers of in-links (good for power-law graphs).
+    ``acc`` is a scratch vector with one float per local vertex; ``plan`` comes from
+    :func:`pagerank_stream_plan` (computed on the fly when missing)."""
+    n = row_ptr.numel() - 1
+    if plan is None:
+        plan = pagerank_stream_plan(row_ptr)
+    _lib.call("pcl_pagerank_pull_stream", row_ptr, cols, contrib, inv_outdeg, n, cols.numel(),
+              plan[0], plan[1], float(damping), acc, new_contrib, new_rank, delta_l1, old_rank,
+              _lib.stream_ptr())

@@ -67,3 +67,64 @@ class MfRatingStream:
             cu += torch.bincount(u, minlength=self.n_users)
             ci += torch.bincount(i, minlength=self.n_items)
         return cu, ci
+
+
+class SparseLrStream:
+    """Rows with ``nnz_row`` features drawn Zipf(s) over ``n_features`` hashed ids (value 1.0);
+    labels Bernoulli(sigmoid(w.x)) for a sparse true w (``w_density`` non-zeros, N(0, 1))."""
+
+    def __init__(self, n_rows: int, n_features: int, nnz_row: int = 40, s: float = 1.05,
+                 w_density: float = 0.01, seed: int = 0, device="cuda", chunk_rows: int = 1 << 20):
+        self.n_rows, self.F, self.k, self.seed = n_rows, n_features, nnz_row, seed
+        self.device = torch.device(device)
+        self.chunk_rows = chunk_rows
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        self.cdf = zipf_cdf(n_features, s, self.device)
+        self.w = torch.zeros(n_features, device=self.device)
+        nz = torch.randperm(n_features, device=self.device, generator=g)[: max(1, int(n_features * w_density))]
+        self.w[nz] = torch.randn(nz.numel(), device=self.device, generator=g)
+
+    def nchunks(self) -> int:
+        return (self.n_rows + self.chunk_rows - 1) // self.chunk_rows
+
+    def chunk_at(self, c: int):
+        """(cols int32 [m * k], y fp32 [m]) of chunk c."""
+        m = min(self.chunk_rows, self.n_rows - c * self.chunk_rows)
+        g = torch.Generator(device=self.device)
+        g.manual_seed(self.seed * 1000003 + 11 + c)
+        cols = zipf_draw(self.cdf, m * self.k, g).view(m, self.k)
+        z = self.w[cols].sum(1)
+        y = (torch.rand(m, device=self.device, generator=g) < torch.sigmoid(z)).float()
+        return cols.to(torch.int32).reshape(-1), y
+
+
+def lda_corpus_chunk(n_docs: int, vocab: int, s: float, mean_len: float, seed: int, device):
+    """(doc_ptr int64, word ids int64) for ``n_docs`` documents: lengths Poisson(mean_len)
+    (at least 1), word ids Zipf(s)."""
+    device = torch.device(device)
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    lens = torch.poisson(torch.full((n_docs,), float(mean_len), device=device), generator=g).long().clamp(min=1)
+    ptr = torch.zeros(n_docs + 1, dtype=torch.int64, device=device)
+    ptr[1:] = torch.cumsum(lens, 0)
+    cdf = zipf_cdf(vocab, s, device)
+    words = zipf_draw(cdf, int(ptr[-1].item()), g)
+    return ptr, words
+
+
+def rmat_edges_chunk(scale: int, m: int, a: float, b: float, c: float, seed: int, device):
+    """``m`` edges of an R-MAT graph with 2^scale vertices (quadrant probabilities a, b, c,
+    1-a-b-c): (src, dst) int64."""
+    device = torch.device(device)
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    src = torch.zeros(m, dtype=torch.int64, device=device)
+    dst = torch.zeros(m, dtype=torch.int64, device=device)
+    for lvl in range(scale):
+        r = torch.rand(m, device=device, generator=g)
+        right = ((r >= a) & (r < a + b)) | (r >= a + b + c)     # quadrants b and d: dst bit set
+        down = r >= a + b                                        # quadrants c and d: src bit set
+        src = (src << 1) | down.long()
+        dst = (dst << 1) | right.long()
+    return src, dst

@@ -109,14 +109,30 @@ def test_pagerank_pull_matches_dense_reference():
         newc = torch.empty(n, device=dev)
         newr = torch.empty(n, device=dev)
         dl = torch.zeros(1, device=dev, dtype=torch.float64)
-        pagerank_pull(row_ptr, cols, contrib, inv, 0.85, newc, newr, dl, pr, threads_per_row=tpr)
+        deg = row_ptr[1:] - row_ptr[:-1]
+        heavy = torch.nonzero(deg > 40).flatten().int().contiguous() if tpr == 8 else None
+        pagerank_pull(row_ptr, cols, contrib, inv, 0.85, newc, newr, dl, pr, threads_per_row=tpr,
+                      heavy_rows=heavy, heavy_deg=40)
         torch.cuda.synchronize()
         ref = torch.zeros(n, device=dev, dtype=torch.float64)
         ref.index_add_(0, dst, contrib.double()[src])
         ref = 0.15 + 0.85 * ref
         torch.testing.assert_close(newr.double(), ref, rtol=1e-5, atol=1e-6)
         torch.testing.assert_close(newc, newr * inv, rtol=1e-6, atol=1e-8)
-        assert abs(float(dl.item()) - float((ref - pr.double()).abs().sum())) < 1e-3
+        tot = float((ref - pr.double()).abs().sum())
+        assert abs(float(dl.item()) - tot) < 1e-5 * tot + 1e-6
+    # edge-balanced variant: blocks own equal numbers of in-links, rows cut by block boundaries
+    from paracel_b200.ops.linear import pagerank_pull_stream
+    contrib = pr * inv
+    acc = torch.full((n,), 7.0, device=dev)        # must be cleared by the call
+    newc2 = torch.empty(n, device=dev)
+    newr2 = torch.empty(n, device=dev)
+    dl2 = torch.zeros(1, device=dev, dtype=torch.float64)
+    pagerank_pull_stream(row_ptr, cols, contrib, inv, 0.85, acc, newc2, newr2, dl2, pr)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(newr2.double(), ref, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(newc2, newr2 * inv, rtol=1e-6, atol=1e-8)
+    assert abs(float(dl2.item()) - tot) < 1e-5 * tot + 1e-6
 
 
 def _sparse_problem(dev, n=20000, F=4096, nnz_row=12, seed=0):
