@@ -51,6 +51,7 @@ def parse_args():
     ap.add_argument("--hot-mix", type=float, default=1.0)
     ap.add_argument("--sgd-blocks", type=int, default=0)
     ap.add_argument("--hot-rows", type=int, default=106)
+    ap.add_argument("--variant", type=int, default=0, help="2: experimental 8-lanes-per-rating SGD kernel")
     ap.add_argument("--chunks-per-flush", type=int, default=8)
     ap.add_argument("--zipf-s", type=float, default=1.1)
     return ap.parse_args()
@@ -99,7 +100,8 @@ def main():
     model = Model(args.users, args.items, k=args.rank, alpha=args.alpha, beta=args.beta,
                   rounds=total_rounds, staleness=args.staleness, ssp=True, seed=args.seed,
                   hot_mix=args.hot_mix, sgd_blocks=args.sgd_blocks, device=dev,
-                  hot_rows=args.hot_rows, chunks_per_flush=args.chunks_per_flush)
+                  hot_rows=args.hot_rows, chunks_per_flush=args.chunks_per_flush,
+                  variant=args.variant)
 
     # ---- data: every rank regenerates the same global stream and keeps its block
     stream = MfRatingStream(args.users, args.items, args.nnz, s=args.zipf_s, seed=args.seed,

@@ -250,6 +250,223 @@ __global__ void __launch_bounds__(512, 2) mf_sgd_kernel(MfArgs a) {
   if (a.sse != nullptr && lane == 0 && sse != 0.f) atomicAdd(a.sse, (double)sse);
 }
 
+// Rank-128 variant with 8 lanes per rating: a warp works on four chunks at once, one per
+// group of 8 lanes, and every lane keeps 16 floats of each 128-float row (elements
+// c*32 + l*4 + t, c < 4, t < 4, i.e. four 128-bit loads per row).  A warp-wide instruction thus
+// advances four ratings, which cuts the instructions per rating to about a quarter of the
+// 32-lanes-per-rating form; the rest of the algorithm (register-resident user row, vector
+// reductions for cold item rows, shared-memory replicas of the hot item rows with periodic
+// mixing) is unchanged.  Hot rows are stored with a stride of 132 floats and the four groups
+// visit the four floats of a 16-byte element in rotated order, so that the 32 lanes of one
+// shared-memory atomic hit 32 different banks.
+constexpr int G8_STRIDE = 132;
+
+__global__ void __launch_bounds__(512, 1) mf_sgd_kernel_g8(MfArgs a) {
+  constexpr int D = 128;
+  extern __shared__ float smem[];
+  const int T = a.hot_T;
+  float* hv = smem;                               // T x 132
+  float* hbase = hv + (size_t)T * G8_STRIDE;      // T x 132
+  float* hb = hbase + (size_t)T * G8_STRIDE;      // T
+  float* hbb = hb + T;                            // T
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 3;                        // group within the warp
+  const int l = lane & 7;                         // lane within the group
+  const unsigned gmask = 0xffu << (8 * g);
+  const int gic = (threadIdx.x >> 5) * 4 + g;     // group index within the CTA
+  const int gpc = (blockDim.x >> 5) * 4;          // groups per CTA
+  const float ab = a.alpha * a.beta;
+  float sse = 0.f;
+
+  const long long cta_chunks = a.nchunks > blockIdx.x
+      ? (a.nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const long long iters = (cta_chunks + gpc - 1) / gpc;
+
+  for (long long it = 0; it < iters; ++it) {
+    if (T > 0 && (it % a.cpw) == 0) {
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < T * D; idx += blockDim.x) {
+        const int row = idx >> 7, e = idx & 127;
+        const int sidx = row * G8_STRIDE + e;
+        float* gp = a.H + (size_t)row * D + e;
+        if (it > 0) {
+          const float d = hv[sidx] - hbase[sidx];
+          if (d != 0.f) atomicAdd(gp, d * a.flush_scale);
+        }
+        const float v = __ldcg(gp);
+        hv[sidx] = v;
+        hbase[sidx] = v;
+      }
+      for (int row = threadIdx.x; row < T; row += blockDim.x) {
+        if (it > 0) {
+          const float d = hb[row] - hbb[row];
+          if (d != 0.f) atomicAdd(a.bi + row, d * a.flush_scale);
+        }
+        const float v = __ldcg(a.bi + row);
+        hb[row] = v;
+        hbb[row] = v;
+      }
+      __syncthreads();
+    }
+    const long long c = (long long)blockIdx.x + ((long long)gic + it * gpc) * gridDim.x;
+    const bool active = c < a.nchunks;          // uniform within the group
+    const long long base = active ? c * 32 : 0;
+    int cur_u = -1;
+    float w[16], w0[16];
+    float bu = 0.f, bu0 = 0.f, s_u = 1.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) { w[k] = 0.f; w0[k] = 0.f; }
+
+    int i_nxt = active ? __ldg(a.ri + base) : 0;
+    float si_nxt = active ? __ldg(a.si + i_nxt) : 0.f;
+    float h_nxt[16];
+    float bi_nxt = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) h_nxt[k] = 0.f;
+    if (active && i_nxt >= T) {
+      const float* hp = a.H + (long long)i_nxt * D + l * 4;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        const float4 x = pcl_ldcg4(hp + cc * 32);
+        h_nxt[4 * cc] = x.x; h_nxt[4 * cc + 1] = x.y; h_nxt[4 * cc + 2] = x.z; h_nxt[4 * cc + 3] = x.w;
+      }
+      bi_nxt = __ldcg(a.bi + i_nxt);
+    }
+
+#pragma unroll 1
+    for (int j = 0; j < 32; ++j) {
+      if (!active) break;
+      const int u = __ldg(a.ru + base + j);
+      const float r = __ldg(a.rr + base + j);
+      const int i = i_nxt;
+      const bool hot = i < T;
+      float h[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) h[k] = h_nxt[k];
+      float bi = bi_nxt;
+      const float s_i = si_nxt;
+      if (j + 1 < 32) {
+        i_nxt = __ldg(a.ri + base + j + 1);
+        si_nxt = __ldg(a.si + i_nxt);
+        if (i_nxt >= T) {
+          const float* hp = a.H + (long long)i_nxt * D + l * 4;
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            const float4 x = pcl_ldcg4(hp + cc * 32);
+            h_nxt[4 * cc] = x.x; h_nxt[4 * cc + 1] = x.y; h_nxt[4 * cc + 2] = x.z; h_nxt[4 * cc + 3] = x.w;
+          }
+          bi_nxt = __ldcg(a.bi + i_nxt);
+        }
+      }
+      if (u < 0) continue;  // padding entry (uniform within the group)
+      if (hot) {
+        const float* sp = hv + i * G8_STRIDE + l * 4;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const float4 x = *reinterpret_cast<const float4*>(sp + cc * 32);
+          h[4 * cc] = x.x; h[4 * cc + 1] = x.y; h[4 * cc + 2] = x.z; h[4 * cc + 3] = x.w;
+        }
+        bi = hb[i];
+      }
+      if (u != cur_u) {
+        if (cur_u >= 0) {
+          float* wp = a.W + (long long)cur_u * D + l * 4;
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc)
+            pcl_red_add4(wp + cc * 32, make_float4(s_u * (w[4 * cc] - w0[4 * cc]),
+                                                   s_u * (w[4 * cc + 1] - w0[4 * cc + 1]),
+                                                   s_u * (w[4 * cc + 2] - w0[4 * cc + 2]),
+                                                   s_u * (w[4 * cc + 3] - w0[4 * cc + 3])));
+          if (l == 0) atomicAdd(a.bu + cur_u, s_u * (bu - bu0));
+        }
+        cur_u = u;
+        const float* wp = a.W + (long long)u * D + l * 4;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const float4 x = pcl_ldcg4(wp + cc * 32);
+          w[4 * cc] = x.x; w[4 * cc + 1] = x.y; w[4 * cc + 2] = x.z; w[4 * cc + 3] = x.w;
+        }
+#pragma unroll
+        for (int k = 0; k < 16; ++k) w0[k] = w[k];
+        bu = __ldcg(a.bu + u);
+        bu0 = bu;
+        s_u = __ldg(a.su + u);
+      }
+      float dot = 0.f;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) dot = fmaf(w[k], h[k], dot);
+      dot += __shfl_xor_sync(gmask, dot, 4);
+      dot += __shfl_xor_sync(gmask, dot, 2);
+      dot += __shfl_xor_sync(gmask, dot, 1);
+      float pred = a.mu + bu + bi + dot;
+      pred = fminf(5.f, fmaxf(1.f, pred));
+      const float e = r - pred;
+      sse = fmaf(e, e, sse);
+      const float a2e = 2.f * a.alpha * e;
+      float dh[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const float wk = w[k], hk = h[k];
+        dh[k] = s_i * (a2e * wk - ab * hk);
+        w[k] = wk + (a2e * hk - ab * wk);
+      }
+      const float dbi = s_i * (a2e - ab * bi);
+      bu += a2e - ab * bu;
+      if (hot) {
+        float* sp = hv + i * G8_STRIDE + l * 4;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+          for (int tt = 0; tt < 4; ++tt) {
+            const int t = (tt + g) & 3;   // rotated per group: 32 lanes -> 32 banks
+            // dh index must be a compile-time constant per unrolled iteration: select by t
+            const float v = (t == 0) ? dh[4 * cc] : (t == 1) ? dh[4 * cc + 1]
+                          : (t == 2) ? dh[4 * cc + 2] : dh[4 * cc + 3];
+            atomicAdd(sp + cc * 32 + t, v);
+          }
+        }
+        if (l == 0) atomicAdd(&hb[i], dbi);
+      } else {
+        float* hp = a.H + (long long)i * D + l * 4;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc)
+          pcl_red_add4(hp + cc * 32, make_float4(dh[4 * cc], dh[4 * cc + 1], dh[4 * cc + 2], dh[4 * cc + 3]));
+        if (l == 0) atomicAdd(a.bi + i, dbi);
+        if (j + 1 < 32 && i_nxt == i) {  // the prefetched copy predates this update
+#pragma unroll
+          for (int k = 0; k < 16; ++k) h_nxt[k] += dh[k];
+          bi_nxt += dbi;
+        }
+      }
+    }
+    if (cur_u >= 0) {
+      float* wp = a.W + (long long)cur_u * D + l * 4;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc)
+        pcl_red_add4(wp + cc * 32, make_float4(s_u * (w[4 * cc] - w0[4 * cc]),
+                                               s_u * (w[4 * cc + 1] - w0[4 * cc + 1]),
+                                               s_u * (w[4 * cc + 2] - w0[4 * cc + 2]),
+                                               s_u * (w[4 * cc + 3] - w0[4 * cc + 3])));
+      if (l == 0) atomicAdd(a.bu + cur_u, s_u * (bu - bu0));
+    }
+  }
+  if (T > 0) {  // final flush of the hot replicas
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < T * D; idx += blockDim.x) {
+      const int row = idx >> 7, e = idx & 127;
+      const int sidx = row * G8_STRIDE + e;
+      const float d = hv[sidx] - hbase[sidx];
+      if (d != 0.f) atomicAdd(a.H + (size_t)row * D + e, d * a.flush_scale);
+    }
+    for (int row = threadIdx.x; row < T; row += blockDim.x) {
+      const float d = hb[row] - hbb[row];
+      if (d != 0.f) atomicAdd(a.bi + row, d * a.flush_scale);
+    }
+  }
+  // every lane of a group saw the same errors: one lane per group reports
+  if (a.sse != nullptr && l == 0 && sse != 0.f) atomicAdd(a.sse, (double)sse);
+}
+
 struct RmseArgs {
   const int* ru;
   const int* ri;
@@ -313,12 +530,14 @@ __global__ void __launch_bounds__(256) mf_rmse_kernel(RmseArgs a) {
 // update rule).  `blocks` <= 0 selects 2 CTAs of 512 threads per SM.  Local
 // item indices below `hot_T` are served from shared-memory replicas that are
 // mixed into the global rows every `cpw` chunks per warp with weight
-// `flush_scale` (<= 0: 1 / blocks).
+// `flush_scale` (<= 0: 1 / blocks).  `variant` 2 (D = 128 only) selects the experimental
+// 8-lanes-per-rating kernel (one CTA per SM, up to 211 hot rows); measured slower than the
+// default because its four groups per warp diverge on the hot / cold / user-switch branches.
 PCL_API int pcl_mf_sgd_pass(const int* ru, const int* ri, const float* rr, long long nnz,
                             float* W, float* H, float* bu, float* bi, const float* su,
                             const float* si, int D, float mu, float alpha, float beta,
                             int hot_T, int cpw, float flush_scale, int blocks, double* sse,
-                            cudaStream_t stream) {
+                            int variant, cudaStream_t stream) {
   if (nnz <= 0) return 0;
   if (nnz % 32 != 0 || hot_T < 0) return (int)cudaErrorInvalidValue;
   MfArgs a;
@@ -331,13 +550,23 @@ PCL_API int pcl_mf_sgd_pass(const int* ru, const int* ri, const float* rr, long 
   a.hot_T = hot_T;
   a.cpw = cpw > 0 ? cpw : 8;
   const int threads = 512;
-  if (blocks <= 0) blocks = 148 * 2;
-  long long need = (a.nchunks + (threads / 32) - 1) / (threads / 32);
+  const bool g8 = (D == 128 && variant == 2);   // variant 2 selects the 8-lanes-per-rating kernel
+  if (blocks <= 0) blocks = g8 ? 148 : 148 * 2;
+  const int units = g8 ? (threads / 32) * 4 : (threads / 32);  // chunks in flight per CTA
+  long long need = (a.nchunks + units - 1) / units;
   if (need < blocks) blocks = (int)need;
   a.flush_scale = flush_scale > 0.f ? flush_scale : 1.f / (float)blocks;
   size_t smem = (size_t)hot_T * (2 * (size_t)D + 2) * sizeof(float);
-  if (smem > 110 * 1024) return (int)cudaErrorInvalidValue;
   cudaError_t e = cudaSuccess;
+  if (g8) {
+    smem = (size_t)hot_T * (2 * (size_t)G8_STRIDE + 2) * sizeof(float);
+    if (smem > 220 * 1024) return (int)cudaErrorInvalidValue;
+    e = cudaFuncSetAttribute(mf_sgd_kernel_g8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    mf_sgd_kernel_g8<<<blocks, threads, smem, stream>>>(a);
+    return pcl_last_error();
+  }
+  if (smem > 110 * 1024) return (int)cudaErrorInvalidValue;
   switch (D) {
     case 32:
       e = cudaFuncSetAttribute(mf_sgd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

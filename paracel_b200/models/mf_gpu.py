@@ -80,7 +80,7 @@ class MfSgdGpu:
                  beta: float = 0.02, rounds: int = 1, staleness: int = 2, ssp: bool = True,
                  group=None, device=None, seed: int = 0, hot_mix: float = 1.0,
                  sgd_blocks: int = 0, timeout_s: float = 5.0, hot_rows: int = 106,
-                 chunks_per_flush: int = 8):
+                 chunks_per_flush: int = 8, variant: int = 0):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -94,8 +94,12 @@ class MfSgdGpu:
         self.ssp = bool(ssp)
         self.seed = seed
         self.hot_mix = float(hot_mix)
-        self.sgd_blocks = int(sgd_blocks) if sgd_blocks > 0 else 148 * 2
-        self.warps_per_block = 16
+        # default: 32-lanes-per-rating kernel, 2 CTAs per SM with 16 chunks in flight each;
+        # variant 2 (D = 128): experimental 8-lanes-per-rating kernel, 1 CTA per SM, 64 chunks
+        self.variant = int(variant)
+        self.g8 = (self.D == 128 and self.variant == 2)
+        self.sgd_blocks = int(sgd_blocks) if sgd_blocks > 0 else (148 if self.g8 else 148 * 2)
+        self.warps_per_block = 64 if self.g8 else 16   # chunks in flight per CTA
         self.hot_rows = int(hot_rows)
         self.chunks_per_flush = int(chunks_per_flush)
         self.npx, self.npy = npfact2d(self.world)
@@ -143,7 +147,7 @@ class MfSgdGpu:
         # take the first local indices and are replicated in shared memory
         conc = P * ci.to(torch.float64) / max(nnz, 1)
         T = int(min(self.hot_rows, int((conc > 1.0).sum().item()), self.li.numel()))
-        T = min(T, (110 * 1024) // ((2 * self.D + 2) * 4))
+        T = min(T, (220 * 1024) // ((2 * 132 + 2) * 4) if self.g8 else (110 * 1024) // ((2 * self.D + 2) * 4))
         self.hot_T = T
         if T > 0:
             hot = torch.topk(ci, T).indices
@@ -269,7 +273,7 @@ class MfSgdGpu:
             _lib.call("pcl_mf_sgd_pass", self.ru, self.ri, self.rr, self.ru.numel(), self.Wl,
                       self.Hl, self.bul, self.bil, self.su, self.si, self.D, self.mu,
                       self.alpha, self.beta, self.hot_T, self.chunks_per_flush, 0.0,
-                      self.sgd_blocks, self.sse, s)
+                      self.sgd_blocks, self.sse, self.variant, s)
         else:
             self._sgd_pass_streamed()
 
@@ -304,7 +308,8 @@ class MfSgdGpu:
             main.wait_event(self._copied[b])
             _lib.call("pcl_mf_sgd_pass", bru, bri, brr, m, self.Wl, self.Hl, self.bul, self.bil,
                       self.su, self.si, self.D, self.mu, self.alpha, self.beta, self.hot_T,
-                      self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, main.cuda_stream)
+                      self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, self.variant,
+                      main.cuda_stream)
             self._consumed[b].record(main)
             k += 1
 

@@ -121,12 +121,14 @@ def test_mf_single_chunk_matches_sequential_oracle():
     from paracel_b200.models.mf_gpu import MfSgdGpu
     dev = "cuda:0"
     g = torch.Generator().manual_seed(3)
-    for k, hot in ((32, 64), (80, 64), (128, 64), (128, 0), (64, 3)):
+    for k, hot, variant in ((32, 64, 0), (80, 64, 0), (128, 64, 0), (128, 0, 0), (64, 3, 0),
+                            (128, 64, 2), (100, 0, 2), (128, 4, 2)):
         nu, ni, nnz = 6, 9, 31
         u = torch.randint(0, nu, (nnz,), generator=g)
         i = torch.randint(0, ni, (nnz,), generator=g)
         r = torch.randint(1, 6, (nnz,), generator=g).float()
-        m = MfSgdGpu(nu, ni, k=k, alpha=0.05, beta=0.02, rounds=1, device=dev, hot_rows=hot)
+        m = MfSgdGpu(nu, ni, k=k, alpha=0.05, beta=0.02, rounds=1, device=dev, hot_rows=hot,
+                     variant=variant)
         m.load_ratings(u, i, r)
         m.init_parameters()
         assert torch.all(m.su == 1) and torch.all(m.si == 1)
@@ -152,7 +154,15 @@ def test_mf_converges_like_sequential_pass():
     from paracel_b200.models.mf_gpu import MfSgdGpu
     from paracel_b200.utils.synth import MfRatingStream
     dev = "cuda:0"
-    nu, ni, nnz, k = 2000, 600, 30_000, 32
+    _converges(32)
+    _converges(128)
+
+
+def _converges(k):
+    from paracel_b200.models.mf_gpu import MfSgdGpu
+    from paracel_b200.utils.synth import MfRatingStream
+    dev = "cuda:0"
+    nu, ni, nnz = 2000, 600, 30_000
     st = MfRatingStream(nu, ni, nnz, seed=5, device=dev)
     u, i, r = st.chunk_at(0)
     rounds = 4
