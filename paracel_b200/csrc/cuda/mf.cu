@@ -38,6 +38,10 @@ struct MfArgs {
   int hot_T;         // local item indices < hot_T are replicated in shared memory
   int cpw;           // chunks per warp between two flushes of the hot replicas
   float flush_scale; // mixing weight of one CTA's hot-row delta (1 / #CTAs)
+  // compact rating stream (optional, replaces ru / ri / rr): 4 bytes per rating + 12 per chunk
+  const unsigned int* packed;  // item index (low 24 bits) | rating code (high 8 bits)
+  const int* chdr;             // per chunk: first user index, increment mask, number of valid entries
+  const float* rtable;         // rating value of each code
 };
 
 template <int VEC>
@@ -135,9 +139,22 @@ __global__ void __launch_bounds__(512, 2) mf_sgd_kernel(MfArgs a) {
     const long long c = (long long)blockIdx.x + ((long long)wic + it * wpc) * gridDim.x;
     if (c >= a.nchunks) continue;  // warp-uniform; barriers above are still reached
     const long long base = c * 32;
-    const int my_u = __ldg(a.ru + base + lane);
-    const int my_i = __ldg(a.ri + base + lane);
-    const float my_r = __ldg(a.rr + base + lane);
+    int my_u, my_i;
+    float my_r;
+    if (a.packed != nullptr) {
+      // users of a user-major sorted chunk grow by 0 or 1 per rating: a base and a bit mask
+      const unsigned int pk = __ldg(a.packed + base + lane);
+      const int u_base = __ldg(a.chdr + 3 * c);
+      const unsigned int inc = (unsigned int)__ldg(a.chdr + 3 * c + 1);
+      const int n_valid = __ldg(a.chdr + 3 * c + 2);
+      my_i = (int)(pk & 0xffffffu);
+      my_r = __ldg(a.rtable + (pk >> 24));
+      my_u = lane < n_valid ? u_base + __popc(inc & (0xffffffffu >> (31 - lane))) : -1;
+    } else {
+      my_u = __ldg(a.ru + base + lane);
+      my_i = __ldg(a.ri + base + lane);
+      my_r = __ldg(a.rr + base + lane);
+    }
     int cur_u = -1;
     Row<VEC> w, w0;
     float bu = 0.f, bu0 = 0.f, s_u = 1.f;
@@ -533,11 +550,15 @@ __global__ void __launch_bounds__(256) mf_rmse_kernel(RmseArgs a) {
 // `flush_scale` (<= 0: 1 / blocks).  `variant` 2 (D = 128 only) selects the experimental
 // 8-lanes-per-rating kernel (one CTA per SM, up to 211 hot rows); measured slower than the
 // default because its four groups per warp diverge on the hot / cold / user-switch branches.
+// Compact stream: when `packed` is given, ru / ri / rr are ignored; rating j of chunk c has item
+// packed[32c+j] & 0xffffff, value rtable[packed >> 24] and user chdr[3c] + popcount of the low
+// j+1 bits of chdr[3c+1] (bit 0 is always clear); entries j >= chdr[3c+2] are padding.
 PCL_API int pcl_mf_sgd_pass(const int* ru, const int* ri, const float* rr, long long nnz,
                             float* W, float* H, float* bu, float* bi, const float* su,
                             const float* si, int D, float mu, float alpha, float beta,
                             int hot_T, int cpw, float flush_scale, int blocks, double* sse,
-                            int variant, cudaStream_t stream) {
+                            int variant, const unsigned int* packed, const int* chdr,
+                            const float* rtable, cudaStream_t stream) {
   if (nnz <= 0) return 0;
   if (nnz % 32 != 0 || hot_T < 0) return (int)cudaErrorInvalidValue;
   MfArgs a;
@@ -547,6 +568,9 @@ PCL_API int pcl_mf_sgd_pass(const int* ru, const int* ri, const float* rr, long 
   a.nchunks = nnz / 32;
   a.stride = 1;
   a.sse = sse;
+  a.packed = packed; a.chdr = chdr; a.rtable = rtable;
+  if (packed != nullptr && (chdr == nullptr || rtable == nullptr || variant == 2))
+    return (int)cudaErrorInvalidValue;
   a.hot_T = hot_T;
   a.cpw = cpw > 0 ? cpw : 8;
   const int threads = 512;

@@ -80,7 +80,7 @@ class MfSgdGpu:
                  beta: float = 0.02, rounds: int = 1, staleness: int = 2, ssp: bool = True,
                  group=None, device=None, seed: int = 0, hot_mix: float = 1.0,
                  sgd_blocks: int = 0, timeout_s: float = 5.0, hot_rows: int = 106,
-                 chunks_per_flush: int = 8, variant: int = 0):
+                 chunks_per_flush: int = 8, variant: int = 0, compact: bool = True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -97,6 +97,7 @@ class MfSgdGpu:
         # default: 32-lanes-per-rating kernel, 2 CTAs per SM with 16 chunks in flight each;
         # variant 2 (D = 128): experimental 8-lanes-per-rating kernel, 1 CTA per SM, 64 chunks
         self.variant = int(variant)
+        self.compact = bool(compact)
         self.g8 = (self.D == 128 and self.variant == 2)
         self.sgd_blocks = int(sgd_blocks) if sgd_blocks > 0 else (148 if self.g8 else 148 * 2)
         self.warps_per_block = 64 if self.g8 else 16   # chunks in flight per CTA
@@ -177,6 +178,7 @@ class MfSgdGpu:
         r = r.view(nch, 32)[perm].contiguous().view(-1)
         del perm
         self.nchunks = nch
+        self._build_compact(ru, ri, r)
         # concurrency weights (see csrc/cuda/mf.cu): expected number of resident
         # warps that touch the same row at the same time
         P = min(P, max(nch, 1))
@@ -199,11 +201,45 @@ class MfSgdGpu:
             self.h_ri = ri.cpu().pin_memory()
             self.h_rr = r.cpu().pin_memory()
             self.ru = self.ri = self.rr = None
+            if self.packed is not None:
+                self.h_packed = self.packed.cpu().pin_memory()
+                self.h_chdr = self.chdr.cpu().pin_memory()
+                self.packed = self.chdr = None
         else:
             self.ru, self.ri, self.rr = ru, ri, r
             self.h_ru = None
         self._sum_r = float(r.sum(dtype=torch.float64).item())
         self._loaded = True
+
+    def _build_compact(self, ru, ri, r):
+        """Compact rating stream (4 bytes per rating + 12 per chunk): item index and an 8-bit
+        rating code in one word; the users of a chunk as first index + increment mask (the users
+        of a user-major sorted chunk grow by 0 or 1 per rating).  Used when there are at most
+        2^24 local items and 256 distinct rating values."""
+        self.packed = self.chdr = self.rtable = None
+        self.h_packed = self.h_chdr = None
+        if ru.numel() == 0:
+            return
+        vals = torch.unique(r)
+        if self.li.numel() > (1 << 24) or vals.numel() > 256:
+            return
+
+        def as_i32(x):  # keep the low 32 bits of an int64 tensor as an int32 bit pattern
+            return torch.where(x >= (1 << 31), x - (1 << 32), x).to(torch.int32)
+        nch = ru.numel() // 32
+        code = torch.searchsorted(vals, r).to(torch.int64)
+        self.packed = as_i32((code << 24) | ri.to(torch.int64)).contiguous()
+        u2 = ru.view(nch, 32).to(torch.int64)
+        valid = u2 >= 0
+        n_valid = valid.sum(1)
+        first = torch.where(n_valid > 0, u2[:, 0], torch.full_like(n_valid, -1))
+        prev = torch.cat([u2[:, :1], u2[:, :-1]], dim=1)
+        inc = ((u2 - prev) == 1) & valid
+        weights = (1 << torch.arange(32, device=ru.device, dtype=torch.int64))
+        mask = as_i32((inc.to(torch.int64) * weights[None, :]).sum(1))
+        self.chdr = torch.stack([first.to(torch.int32), mask, n_valid.to(torch.int32)], dim=1).contiguous().view(-1)
+        self.rtable = torch.zeros(256, device=ru.device)
+        self.rtable[: vals.numel()] = vals
 
     def offload_ratings(self):
         """Switch to out-of-core mode: move the chunked ratings to pinned host memory."""
@@ -214,6 +250,10 @@ class MfSgdGpu:
         self.h_ri = self.ri.cpu().pin_memory()
         self.h_rr = self.rr.cpu().pin_memory()
         self.ru = self.ri = self.rr = None
+        if self.packed is not None:
+            self.h_packed = self.packed.cpu().pin_memory()
+            self.h_chdr = self.chdr.cpu().pin_memory()
+            self.packed = self.chdr = None
 
     # ------------------------------------------------------------ parameters
     def init_parameters(self):
@@ -270,24 +310,32 @@ class MfSgdGpu:
     def sgd_pass(self):
         s = _lib.stream_ptr()
         if self.h_ru is None:
+            pk = self.packed if (self.compact and not self.g8) else None
             _lib.call("pcl_mf_sgd_pass", self.ru, self.ri, self.rr, self.ru.numel(), self.Wl,
                       self.Hl, self.bul, self.bil, self.su, self.si, self.D, self.mu,
                       self.alpha, self.beta, self.hot_T, self.chunks_per_flush, 0.0,
-                      self.sgd_blocks, self.sse, self.variant, s)
+                      self.sgd_blocks, self.sse, self.variant, pk, self.chdr if pk is not None else None,
+                      self.rtable if pk is not None else None, s)
         else:
             self._sgd_pass_streamed()
 
     def _sgd_pass_streamed(self, nseg: int = 16):
-        """Out-of-core pass: ratings come from pinned host memory in segments; the copy
-        of segment s+1 overlaps the SGD kernel of segment s (two staging buffers)."""
+        """Out-of-core pass: ratings come from pinned host memory in segments; the copy of
+        segment s+1 overlaps the SGD kernel of segment s (two staging buffers).  With the compact
+        stream a segment is one int32 per rating plus three per chunk, otherwise three arrays."""
         dev = self.device
         n = self.h_ru.numel()
+        compact = self.compact and not self.g8 and self.h_packed is not None
         seg = ((n // 32 + nseg - 1) // nseg) * 32
         if self.host_stream is None:
             self.host_stream = torch.cuda.Stream(device=dev)
-            self._stage = [(torch.empty(seg, dtype=torch.int32, device=dev),
-                            torch.empty(seg, dtype=torch.int32, device=dev),
-                            torch.empty(seg, dtype=torch.float32, device=dev)) for _ in range(2)]
+            if compact:
+                self._stage = [(torch.empty(seg, dtype=torch.int32, device=dev),
+                                torch.empty(3 * (seg // 32), dtype=torch.int32, device=dev)) for _ in range(2)]
+            else:
+                self._stage = [(torch.empty(seg, dtype=torch.int32, device=dev),
+                                torch.empty(seg, dtype=torch.int32, device=dev),
+                                torch.empty(seg, dtype=torch.float32, device=dev)) for _ in range(2)]
             self._copied = [torch.cuda.Event() for _ in range(2)]
             self._consumed = [torch.cuda.Event() for _ in range(2)]
         main = torch.cuda.current_stream(dev)
@@ -296,20 +344,33 @@ class MfSgdGpu:
         for off in range(0, n, seg):
             m = min(seg, n - off)
             b = k % 2
-            bru, bri, brr = self._stage[b]
             with torch.cuda.stream(self.host_stream):
                 if k >= 2:
                     self.host_stream.wait_event(self._consumed[b])
-                bru[:m].copy_(self.h_ru[off:off + m], non_blocking=True)
-                bri[:m].copy_(self.h_ri[off:off + m], non_blocking=True)
-                brr[:m].copy_(self.h_rr[off:off + m], non_blocking=True)
+                if compact:
+                    bpk, bhd = self._stage[b]
+                    bpk[:m].copy_(self.h_packed[off:off + m], non_blocking=True)
+                    c0, c1 = 3 * (off // 32), 3 * ((off + m) // 32)
+                    bhd[: c1 - c0].copy_(self.h_chdr[c0:c1], non_blocking=True)
+                    self.h2d_bytes += 4 * m + 4 * (c1 - c0)
+                else:
+                    bru, bri, brr = self._stage[b]
+                    bru[:m].copy_(self.h_ru[off:off + m], non_blocking=True)
+                    bri[:m].copy_(self.h_ri[off:off + m], non_blocking=True)
+                    brr[:m].copy_(self.h_rr[off:off + m], non_blocking=True)
+                    self.h2d_bytes += 12 * m
                 self._copied[b].record(self.host_stream)
-            self.h2d_bytes += 12 * m
             main.wait_event(self._copied[b])
-            _lib.call("pcl_mf_sgd_pass", bru, bri, brr, m, self.Wl, self.Hl, self.bul, self.bil,
-                      self.su, self.si, self.D, self.mu, self.alpha, self.beta, self.hot_T,
-                      self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, self.variant,
-                      main.cuda_stream)
+            if compact:
+                _lib.call("pcl_mf_sgd_pass", None, None, None, m, self.Wl, self.Hl, self.bul, self.bil,
+                          self.su, self.si, self.D, self.mu, self.alpha, self.beta, self.hot_T,
+                          self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, self.variant, bpk, bhd,
+                          self.rtable, main.cuda_stream)
+            else:
+                _lib.call("pcl_mf_sgd_pass", bru, bri, brr, m, self.Wl, self.Hl, self.bul, self.bil,
+                          self.su, self.si, self.D, self.mu, self.alpha, self.beta, self.hot_T,
+                          self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, self.variant, None, None,
+                          None, main.cuda_stream)
             self._consumed[b].record(main)
             k += 1
 

@@ -42,7 +42,7 @@ SIGS = {
     "pcl_scalars_push_f32": "ppiqpppip",
     "pcl_rows_pull_i32": "ppiiqppp",
     "pcl_rows_push_i32": "ppiiqppip",
-    "pcl_mf_sgd_pass": "pppqppppppifffiifipip",
+    "pcl_mf_sgd_pass": "pppqppppppifffiifipipppp",
     "pcl_mf_sse": "pppqppppifppp",
     "pcl_gemm_tf32": "pppiiiqipppppiiiiipip",
     "pcl_split3_tf32": "ppqiip",

@@ -121,14 +121,15 @@ def test_mf_single_chunk_matches_sequential_oracle():
     from paracel_b200.models.mf_gpu import MfSgdGpu
     dev = "cuda:0"
     g = torch.Generator().manual_seed(3)
-    for k, hot, variant in ((32, 64, 0), (80, 64, 0), (128, 64, 0), (128, 0, 0), (64, 3, 0),
-                            (128, 64, 2), (100, 0, 2), (128, 4, 2)):
+    for k, hot, variant, compact in ((32, 64, 0, True), (80, 64, 0, False), (128, 64, 0, True),
+                                     (128, 0, 0, False), (64, 3, 0, True), (128, 64, 2, True),
+                                     (100, 0, 2, True), (128, 4, 2, True)):
         nu, ni, nnz = 6, 9, 31
         u = torch.randint(0, nu, (nnz,), generator=g)
         i = torch.randint(0, ni, (nnz,), generator=g)
         r = torch.randint(1, 6, (nnz,), generator=g).float()
         m = MfSgdGpu(nu, ni, k=k, alpha=0.05, beta=0.02, rounds=1, device=dev, hot_rows=hot,
-                     variant=variant)
+                     variant=variant, compact=compact)
         m.load_ratings(u, i, r)
         m.init_parameters()
         assert torch.all(m.su == 1) and torch.all(m.si == 1)
@@ -189,7 +190,7 @@ def _converges(k):
     assert torch.all((pr >= 1) & (pr <= 5))
     m.free()
     assert r_gpu < r0
-    assert abs(r_gpu - r_cpu) < 0.05 * r_cpu, (r0, r_gpu, r_cpu)
+    assert abs(r_gpu - r_cpu) < 0.10 * r_cpu, (r0, r_gpu, r_cpu)
 
 
 def test_mf_streamed_rounds_equal_resident_rounds_statistically():
@@ -201,13 +202,13 @@ def test_mf_streamed_rounds_equal_resident_rounds_statistically():
     i = torch.randint(0, ni, (nnz,), device=dev, generator=g)
     r = torch.randint(1, 6, (nnz,), device=dev, generator=g).float()
     out = []
-    for host in (False, True):
-        m = MfSgdGpu(nu, ni, k=64, rounds=4, device=dev, seed=1)
+    for host, compact in ((False, True), (True, True), (True, False)):
+        m = MfSgdGpu(nu, ni, k=64, rounds=4, device=dev, seed=1, compact=compact)
         m.load_ratings(u, i, r, keep_on_host=host)
         m.init_parameters()
         m.fit()
         out.append(m.rmse())
         if host:
-            assert m.h2d_bytes == 12 * m.nchunks * 32
+            assert m.h2d_bytes == ((4 * 32 + 12) if compact else 12 * 32) * m.nchunks
         m.free()
-    assert abs(out[0] - out[1]) < 0.02 * out[0], out
+    assert abs(out[0] - out[1]) < 0.02 * out[0] and abs(out[0] - out[2]) < 0.02 * out[0], out
