@@ -159,9 +159,11 @@ def main():
         return float(ms.item()), _lib.launches() - l0, last
 
     # ---- device-timed: ratings resident in HBM
+    # clocks are sampled every 50 ms from the first warm-up step to the end of the timed steps
+    # (a timed region of a few steps can be shorter than one sampling period)
+    sampler = ClockSampler(local_rank, period_ms=50).start() if rank == 0 else None
     for _ in range(Wm):
         model.round()
-    sampler = ClockSampler(local_rank).start() if rank == 0 else None
     ms, launches, _ = timed(K, False)
     clocks = sampler.stop() if sampler else None
     model.clock.check()

@@ -34,6 +34,13 @@ class ClockSampler:
     def stop(self) -> Dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        # one more blocking sample while the GPU is still under the load that was just timed
+        try:
+            extra = subprocess.run([shutil.which("nvidia-smi"), "-i", str(self.gpu_index),
+                                    f"--query-gpu={_QUERY}", "--format=csv,noheader,nounits"],
+                                   capture_output=True, text=True, timeout=10).stdout
+        except Exception:  # noqa: BLE001
+            extra = ""
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -41,7 +48,8 @@ class ClockSampler:
             self.proc.kill()
         self.tmp.flush()
         self.tmp.seek(0)
-        rows: List[List[str]] = [[c.strip() for c in ln.split(",")] for ln in self.tmp if ln.strip()]
+        rows: List[List[str]] = [[c.strip() for c in ln.split(",")] for ln in list(self.tmp) + extra.splitlines()
+                                 if ln.strip()]
         self.tmp.close()
         sm, mx, pw = [], [], []
         reasons = set()
