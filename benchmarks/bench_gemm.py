@@ -36,22 +36,27 @@ def main():
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=128)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--kernel", default="2sm", choices=["1sm", "2sm"],
+                    help="1sm: one CTA per 128x128 tile; 2sm: CTA pairs on 256x256 tiles")
     args = ap.parse_args()
-    from paracel_b200.ops.gemm import argmin_nt, gemm_nt
+    from paracel_b200.ops.gemm import argmin_nt, check_status, gemm_nt
     dev = "cuda"
     A = torch.randn(args.m, args.k, device=dev)
     B = torch.randn(args.n, args.k, device=dev)
     C = torch.empty(args.m, args.n, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
     flops = 2.0 * args.m * args.n * args.k
-    out = {"m": args.m, "n": args.n, "k": args.k}
-    t = timeit(lambda: gemm_nt(A, B, out=C), flush, args.iters)
+    out = {"m": args.m, "n": args.n, "k": args.k, "kernel": args.kernel}
+    kn = args.kernel
+    t = timeit(lambda: gemm_nt(A, B, out=C, kernel=kn), flush, args.iters)
+    check_status()
     out["ours_tf32_ms"] = t
     out["ours_tf32_tflops"] = flops / t / 1e9
-    t = timeit(lambda: gemm_nt(A, B, out=C, precise=True), flush, args.iters)
+    t = timeit(lambda: gemm_nt(A, B, out=C, precise=True, kernel=kn), flush, args.iters)
     out["ours_3xtf32_ms"] = t
-    t = timeit(lambda: argmin_nt(A, B), flush, args.iters)
+    t = timeit(lambda: argmin_nt(A, B, kernel=kn), flush, args.iters)
     out["ours_argmin_ms"] = t
+    check_status()
     torch.backends.cuda.matmul.allow_tf32 = True
     t = timeit(lambda: torch.matmul(A, B.T, out=C), flush, args.iters)
     out["cublas_tf32_ms"] = t

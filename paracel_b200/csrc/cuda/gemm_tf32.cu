@@ -39,7 +39,8 @@ constexpr int STAGES = 6;
 constexpr int UMMA_K = 8;    // tf32
 constexpr int A_BYTES = BM * BK * 4;
 constexpr int B_BYTES = BN * BK * 4;
-constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/ +
+                           4 * BN * 4 /*|b_n|^2 of the current tile, per epilogue warp*/;
 constexpr unsigned SPIN_LIMIT = 1u << 24;
 
 struct GemmArgs {
@@ -180,13 +181,29 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int nt = tile_at(ord, n_tiles, first_local);
       const int r0 = nt * BN;
       const int r1 = min(a.N, r0 + BN);
-      for (long long idx = threadIdx.x; idx < (long long)(r1 - r0) * kv; idx += blockDim.x) {
-        const int row = r0 + (int)(idx / kv);
-        const int c = (int)(idx % kv);
-        const int owner = min(row / a.rows_per_shard, a.world - 1);
-        const float* src = a.b_shards[owner] + (long long)(row - owner * a.rows_per_shard) * a.K + 4 * c;
-        const float4 v = pcl_ld_sys4(src);
-        *reinterpret_cast<float4*>(a.b_stage + (long long)row * a.K + 4 * c) = v;
+      // eight 128-bit peer loads in flight per thread before the first store
+      const long long total = (long long)(r1 - r0) * kv;
+      for (long long base = threadIdx.x; base < total; base += (long long)blockDim.x * 8) {
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const long long idx = base + (long long)u * blockDim.x;
+          if (idx < total) {
+            const int row = r0 + (int)(idx / kv);
+            const int c = (int)(idx % kv);
+            const int owner = min(row / a.rows_per_shard, a.world - 1);
+            v[u] = pcl_ld_sys4(a.b_shards[owner] + (long long)(row - owner * a.rows_per_shard) * a.K + 4 * c);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const long long idx = base + (long long)u * blockDim.x;
+          if (idx < total) {
+            const int row = r0 + (int)(idx / kv);
+            const int c = (int)(idx % kv);
+            *reinterpret_cast<float4*>(a.b_stage + (long long)row * a.K + 4 * c) = v[u];
+          }
+        }
       }
       __syncthreads();
       if (threadIdx.x == 0) {
@@ -321,6 +338,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // epilogue warps 2..5; a warp may only touch the 32 TMEM lanes of its sub-partition
     const int sub = warp & 3;
     const int row_in_tile = sub * 32 + lane;
+    float* bn_s = reinterpret_cast<float*>(base + STAGES * (A_BYTES + B_BYTES) + 256) + (warp - 2) * BN;
     int acc = 0;
     uint32_t acc_phase[2] = {0, 0};
     bool ok = true;
@@ -338,6 +356,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t t0 = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(acc * BN);
+        if (a.epi == 1) {   // |b_n|^2 of this tile's columns, +inf beyond N
+          __syncwarp();
+          for (int q = lane; q < BN; q += 32) {
+            const int n = nt * BN + q;
+            bn_s[q] = n < a.N ? __ldg(a.bnorm + n) : 3.402823466e38f;
+          }
+          __syncwarp();
+        }
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           float v[32];
@@ -356,13 +382,31 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
           } else {
+            // dist[j] = |b_n|^2 - 2 a.b_n; the minimum first (one FMNMX per column), the column
+            // index only when this chunk improves the running best, which becomes rare quickly
+            float d[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int n = n0 + j;
-              if (n < a.N) {
-                const float dist = __ldg(a.bnorm + n) - 2.f * v[j];
-                if (dist < best || (dist == best && n < best_n)) { best = dist; best_n = n; }
-              }
+            for (int q = 0; q < 8; ++q) {
+              const float4 b = *reinterpret_cast<const float4*>(bn_s + c * 32 + 4 * q);
+              d[4 * q] = fmaf(-2.f, v[4 * q], b.x);
+              d[4 * q + 1] = fmaf(-2.f, v[4 * q + 1], b.y);
+              d[4 * q + 2] = fmaf(-2.f, v[4 * q + 2], b.z);
+              d[4 * q + 3] = fmaf(-2.f, v[4 * q + 3], b.w);
+            }
+            float m16[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) m16[j] = fminf(d[j], d[j + 16]);
+#pragma unroll
+            for (int w = 8; w >= 1; w >>= 1)
+#pragma unroll
+              for (int j = 0; j < w; ++j) m16[j] = fminf(m16[j], m16[j + w]);
+            const float m = m16[0];
+            if (m <= best) {
+              int jn = 31;
+#pragma unroll
+              for (int j = 30; j >= 0; --j) jn = (d[j] == m) ? j : jn;
+              const int n = n0 + jn;
+              if (m < best || n < best_n) { best = m; best_n = n; }
             }
           }
         }

@@ -1,0 +1,609 @@
+// C[M x N] = A[M x K] * B[N x K]^T, fp32 storage, tcgen05.mma kind::tf32 with
+// cta_group::2: two CTAs on neighbouring SMs (a cluster of two) work on one
+// 256 x 256 output tile.  Each CTA stages only ITS half of the operands per K
+// step (128 rows of A, 128 rows of B: 32 KB instead of the 64 KB a lone CTA
+// would need for the same number of flops), the tensor cores of both SMs read
+// both halves, and each CTA keeps its 128 x 256 half of the accumulator in its
+// own tensor memory.  Shared-memory traffic per flop is half of the
+// one-CTA kernel in gemm_tf32.cu, which is bound by exactly that traffic.
+//
+// Same contract as pcl_gemm_tf32 (store or k-means arg-min epilogue, fused
+// all-gather of a range-sharded B through a local staging buffer).  Reference
+// call sites that this serves: the centre-distance loop of
+// alg/clustering/kmeans/kmeans.hpp:113-133 and the all-pairs products of
+// alg/recommendation/similarity_dense/sim_dense.hpp:84-101.
+//
+// Roles in each CTA (192 threads):
+//   warp 0      TMA producer for this CTA's operand halves; the transfers of both
+//               CTAs complete on the LEADER's "full" barrier (cta_group::2 form of
+//               cp.async.bulk.tensor, no multicast)
+//   warp 1      tensor-memory allocation (both CTAs); in the leader one lane issues
+//               the M256 N256 K8 MMAs and commits to the barriers of both CTAs
+//   warps 2-5   epilogue on the CTA's own accumulator half: tcgen05.ld, transpose
+//               through swizzled shared memory, coalesced row stores (or arg-min)
+// Every wait has a time limit; on expiry the status record is written, both
+// CTAs of the pair are told to leave, tensor memory is freed and the kernel ends.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TM = 256;      // tile rows per CTA pair
+constexpr int TN = 256;      // tile columns
+constexpr int HM = 128;      // rows of A (and of the accumulator) per CTA
+constexpr int HN = 128;      // rows of B staged per CTA
+constexpr int BK = 32;       // 32 fp32 = 128 bytes = one swizzle row
+constexpr int STAGES = 6;
+constexpr int UMMA_K = 8;
+constexpr int A_BYTES = HM * BK * 4;
+constexpr int B_BYTES = HN * BK * 4;
+constexpr int EPI_BYTES = 4 * 32 * 128;  // one 32 x 32 fp32 chunk per epilogue warp
+constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr unsigned long long WAIT_NS = 2000000000ull;  // 2 s per wait
+
+struct Gemm2Args {
+  float* C;
+  long long ldc;
+  int M, N, K;
+  int epi;
+  const float* bnorm;
+  float* row_min;
+  int* row_arg;
+  const float* const* b_shards;
+  float* b_stage;
+  int* flags;          // one per 256-column tile
+  int world, rank, rows_per_shard, epoch, gather_ctas;
+  PclStatus* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+// arrive on a barrier given by its cluster address (own or peer CTA)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const uint32_t addr = smem_u32(bar);
+  unsigned long long t0 = 0;
+  for (unsigned it = 0;; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((it & 31) == 31) {
+      if (*abort_flag) return false;
+      const unsigned long long now = pcl_globaltimer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_NS) return false;
+    }
+  }
+}
+
+// This CTA's half of an operand; the bytes are counted on the leader's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_cluster, const CUtensorMap* map,
+                                                 uint32_t leader_bar_cluster, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst_cluster), "l"(map), "r"(leader_bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
+  const uint32_t lo = ((saddr >> 4) & 0x3FFFu) | (1u << 16);
+  const uint32_t hi = 64u /*8-row groups 1024 B apart*/ | (1u << 14) | (2u << 29) /*128-byte swizzle*/;
+  return ((uint64_t)hi << 32) | lo;
+}
+
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u),
+      "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+
+// arrive on `cluster_addr` once every MMA issued so far by this thread has finished
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void report(PclStatus* st, int rank, int wait_id, long long expected,
+                                       long long seen) {
+  if (st != nullptr && atomicCAS(&st->code, 0, 1) == 0) {
+    st->rank = rank;
+    st->wait_id = wait_id;
+    st->expected = expected;
+    st->seen = seen;
+  }
+}
+
+__device__ __forceinline__ int tile_at(int ord, int n_tiles, int first_local) {
+  const int t = first_local + ord;
+  return t >= n_tiles ? t - n_tiles : t;
+}
+
+__device__ __forceinline__ void decode_item(long long item, bool flat, int n_tiles, int n_first,
+                                            long long first_items, int& mt, int& ord0, int& ord1) {
+  if (!flat) {
+    mt = (int)item; ord0 = 0; ord1 = n_tiles;
+  } else if (item < first_items) {
+    mt = (int)(item / n_first); ord0 = (int)(item % n_first); ord1 = ord0 + 1;
+  } else {
+    const long long rem = item - first_items;
+    const int n_rest = n_tiles - n_first;
+    mt = (int)(rem / n_rest); ord0 = n_first + (int)(rem % n_rest); ord1 = ord0 + 1;
+  }
+}
+
+// raise the abort flag of both CTAs of the pair
+__device__ __forceinline__ void abort_pair(volatile int* abort_flag, uint32_t peer) {
+  *abort_flag = 1;
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(map_to_cta(smem_u32((const void*)abort_flag), peer)),
+               "r"(1)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(192, 1)
+gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     Gemm2Args a) {
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (a.N + TN - 1) / TN;
+  const int m_tiles = (a.M + TM - 1) / TM;
+  const int kb_count = (a.K + BK - 1) / BK;
+  int first_local = 0;
+  if (a.world > 1) first_local = (int)(((long long)a.rank * a.rows_per_shard) / TN) % n_tiles;
+
+  // ------------------------------------------------- gather CTAs (whole clusters)
+  if ((int)blockIdx.x < a.gather_ctas) {
+    const int kv = a.K >> 2;
+    for (int ord = blockIdx.x; ord < n_tiles; ord += a.gather_ctas) {
+      const int nt = tile_at(ord, n_tiles, first_local);
+      const int r0 = nt * TN;
+      const int r1 = min(a.N, r0 + TN);
+      // eight 128-bit peer loads in flight per thread before the first store
+      const long long total = (long long)(r1 - r0) * kv;
+      for (long long base = threadIdx.x; base < total; base += (long long)blockDim.x * 8) {
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const long long idx = base + (long long)u * blockDim.x;
+          if (idx < total) {
+            const int row = r0 + (int)(idx / kv);
+            const int c = (int)(idx % kv);
+            const int owner = min(row / a.rows_per_shard, a.world - 1);
+            v[u] = pcl_ld_sys4(a.b_shards[owner] + (long long)(row - owner * a.rows_per_shard) * a.K + 4 * c);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const long long idx = base + (long long)u * blockDim.x;
+          if (idx < total) {
+            const int row = r0 + (int)(idx / kv);
+            const int c = (int)(idx % kv);
+            *reinterpret_cast<float4*>(a.b_stage + (long long)row * a.K + 4 * c) = v[u];
+          }
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(a.flags + nt), "r"(a.epoch) : "memory");
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ MMA pairs
+  const uint32_t me = cluster_ctarank();   // 0 = leader
+  const uint32_t peer = me ^ 1u;
+  uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = base;
+  uint8_t* sB = base + STAGES * A_BYTES;
+  uint8_t* sE = base + STAGES * (A_BYTES + B_BYTES);
+  uint64_t* bars = (uint64_t*)(sE + EPI_BYTES);
+  uint64_t* full = bars;                 // STAGES, used in the leader
+  uint64_t* empty = bars + STAGES;       // STAGES, one set per CTA
+  uint64_t* tfull = bars + 2 * STAGES;   // 2, one set per CTA
+  uint64_t* tempty = tfull + 2;          // 2, used in the leader (8 warp arrivals)
+  uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull + b, 1); mbar_init(tempty + b, 8); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)), "r"(2 * TN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything signals them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int pair = ((int)blockIdx.x - a.gather_ctas) >> 1;
+  const int npair = ((int)gridDim.x - a.gather_ctas) >> 1;
+  // Work items: with a stored C every 256 x 256 tile is an item (row-block major, so the pairs
+  // that run together share A and all of B through L2); with the arg-min epilogue an item is a
+  // 256-row block whose pair walks all column tiles (running minimum; local tiles first).
+  const bool flat = (a.epi == 0);
+  const long long items = flat ? (long long)m_tiles * n_tiles : (long long)m_tiles;
+  // With a fused gather the flat order has two phases: every row block against this rank's own
+  // column tiles first (they need no staging), then every row block against the staged tiles.
+  int n_first = n_tiles;
+  if (a.gather_ctas > 0) {
+    const int own_rows = max(0, min(a.rows_per_shard, a.N - a.rank * a.rows_per_shard));
+    n_first = max(1, min(n_tiles, own_rows / TN));
+  }
+  const long long first_items = (long long)m_tiles * n_first;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long item = pair; item < items && ok; item += npair) {
+        int mt, ord0, ord1;
+        decode_item(item, flat, n_tiles, n_first, first_items, mt, ord0, ord1);
+        for (int ord = ord0; ord < ord1 && ok; ++ord) {
+          const int nt = tile_at(ord, n_tiles, first_local);
+          if (a.gather_ctas > 0) {
+            int seen = 0;
+            const unsigned long long t0 = pcl_globaltimer();
+            for (unsigned it = 0;; ++it) {
+              seen = pcl_ld_acquire_sys_i32(a.flags + nt);
+              if (seen == a.epoch || *abort_flag) break;
+              if ((it & 15) == 15 && pcl_globaltimer() - t0 > WAIT_NS) break;
+              __nanosleep(128);
+            }
+            if (seen != a.epoch) {
+              report(a.status, a.rank, 30, a.epoch, seen);
+              abort_pair(abort_flag, peer);
+              ok = false;
+              break;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+          for (int kb = 0; kb < kb_count; ++kb) {
+            if (!mbar_wait(empty + stage, phase ^ 1, abort_flag)) {
+              report(a.status, a.rank, 31, kb, stage);
+              abort_pair(abort_flag, peer);
+              ok = false;
+              break;
+            }
+            if (me == 0) mbar_expect_tx(full + stage, 2 * (A_BYTES + B_BYTES));
+            const uint32_t lbar = map_to_cta(smem_u32(full + stage), 0);
+            tma_load_2d_pair(map_to_cta(smem_u32(sA + stage * A_BYTES), me), &tmA, lbar, kb * BK,
+                             mt * TM + (int)me * HM);
+            tma_load_2d_pair(map_to_cta(smem_u32(sB + stage * B_BYTES), me), &tmB, lbar, kb * BK,
+                             nt * TN + (int)me * HN);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+      if (!ok) {
+        for (int s = 0; s < 2048; ++s) __nanosleep(1000);  // let copies in flight land
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && me == 0) {
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TN >> 3) << 17) |
+                             ((uint32_t)(TM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      bool ok = true;
+      for (long long item = pair; item < items && ok; item += npair) {
+        int mt, ord0, ord1;
+        decode_item(item, flat, n_tiles, n_first, first_items, mt, ord0, ord1);
+        for (int ord = ord0; ord < ord1 && ok; ++ord) {
+          if (!mbar_wait(tempty + acc, acc_phase[acc] ^ 1, abort_flag)) {
+            report(a.status, a.rank, 32, acc, 0);
+            abort_pair(abort_flag, peer);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t d = tmem_base + (uint32_t)(acc * TN);
+          for (int kb = 0; kb < kb_count; ++kb) {
+            if (!mbar_wait(full + stage, phase, abort_flag)) {
+              report(a.status, a.rank, 33, kb, stage);
+              abort_pair(abort_flag, peer);
+              ok = false;
+              break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t da = make_desc_sw128(smem_u32(sA + stage * A_BYTES));
+            const uint64_t db = make_desc_sw128(smem_u32(sB + stage * B_BYTES));
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_tf32_pair(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                             (kb > 0 || k > 0) ? 1u : 0u);
+            // free this stage in both CTAs
+            umma_commit_pair(map_to_cta(smem_u32(empty + stage), 0));
+            umma_commit_pair(map_to_cta(smem_u32(empty + stage), 1));
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          umma_commit_pair(map_to_cta(smem_u32(tfull + acc), 0));
+          umma_commit_pair(map_to_cta(smem_u32(tfull + acc), 1));
+          acc_phase[acc] ^= 1;
+          acc ^= 1;
+        }
+      }
+    }
+  } else {
+    const int sub = warp & 3;                 // tensor-memory sub-partition of this warp
+    float* stg = reinterpret_cast<float*>(sE + (warp - 2) * 4096);
+    const uint32_t tempty_leader0 = map_to_cta(smem_u32(tempty), 0);
+    int acc = 0;
+    uint32_t acc_phase[2] = {0, 0};
+    bool ok = true;
+    for (long long item = pair; item < items && ok; item += npair) {
+      int mt, ord0, ord1;
+      decode_item(item, flat, n_tiles, n_first, first_items, mt, ord0, ord1);
+      const int row_base = mt * TM + (int)me * HM + sub * 32;   // first row of this warp's 32
+      const int row = row_base + lane;
+      float best = 3.402823466e38f;
+      int best_n = 0;
+      for (int ord = ord0; ord < ord1 && ok; ++ord) {
+        const int nt = tile_at(ord, n_tiles, first_local);
+        if (!mbar_wait(tfull + acc, acc_phase[acc], abort_flag)) {
+          if (lane == 0) {
+            report(a.status, a.rank, 34, acc, 0);
+            abort_pair(abort_flag, peer);
+          }
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t t0 = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(acc * TN);
+        const bool vec_ok = ((a.ldc & 3) == 0) && ((((uintptr_t)a.C) & 15) == 0);
+        if (a.epi == 1) {   // |b_n|^2 of this tile's columns, +inf beyond N
+          __syncwarp();
+          for (int q = lane; q < TN; q += 32) {
+            const int n = nt * TN + q;
+            stg[q] = n < a.N ? __ldg(a.bnorm + n) : 3.402823466e38f;
+          }
+          __syncwarp();
+        }
+#pragma unroll 1
+        for (int c = 0; c < TN / 32; ++c) {
+          float v[32];
+          tmem_ld32(t0 + (uint32_t)(c * 32), v);
+          const int n0 = nt * TN + c * 32;
+          if (n0 >= a.N) continue;
+          if (a.epi == 0) {
+            if (n0 + 32 <= a.N && vec_ok) {
+              // transpose through shared memory: lane r wrote row r; afterwards 8 lanes cover
+              // the 128 bytes of one row, so one store instruction writes 4 full lines
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(stg + lane * 32 + ((q ^ (lane & 7)) << 2)) =
+                    make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int r = 4 * i + (lane >> 3);
+                const int q = lane & 7;
+                const float4 x = *reinterpret_cast<const float4*>(stg + r * 32 + ((q ^ (r & 7)) << 2));
+                if (row_base + r < a.M)
+                  *reinterpret_cast<float4*>(a.C + (long long)(row_base + r) * a.ldc + n0 + 4 * q) = x;
+              }
+              __syncwarp();
+            } else if (row < a.M) {
+              float* dst = a.C + (long long)row * a.ldc + n0;
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < a.N) dst[j] = v[j];
+            }
+          } else {
+            // dist[j] = |b_n|^2 - 2 a.b_n; the minimum first (one FMNMX per column), the column
+            // index only when this chunk improves the running best, which becomes rare quickly
+            float d[32];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 b = *reinterpret_cast<const float4*>(stg + c * 32 + 4 * q);
+              d[4 * q] = fmaf(-2.f, v[4 * q], b.x);
+              d[4 * q + 1] = fmaf(-2.f, v[4 * q + 1], b.y);
+              d[4 * q + 2] = fmaf(-2.f, v[4 * q + 2], b.z);
+              d[4 * q + 3] = fmaf(-2.f, v[4 * q + 3], b.w);
+            }
+            float m16[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) m16[j] = fminf(d[j], d[j + 16]);
+#pragma unroll
+            for (int w = 8; w >= 1; w >>= 1)
+#pragma unroll
+              for (int j = 0; j < w; ++j) m16[j] = fminf(m16[j], m16[j + w]);
+            const float m = m16[0];
+            if (m <= best) {
+              int jn = 31;
+#pragma unroll
+              for (int j = 30; j >= 0; --j) jn = (d[j] == m) ? j : jn;
+              const int n = n0 + jn;
+              if (m < best || n < best_n) { best = m; best_n = n; }
+            }
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty_leader0 + (uint32_t)(acc * 8));
+        acc_phase[acc] ^= 1;
+        acc ^= 1;
+      }
+      if (ok && a.epi == 1 && row < a.M) {
+        a.row_min[row] = best;
+        a.row_arg[row] = best_n;
+      }
+    }
+  }
+
+  // nobody leaves while the peer may still read this CTA's shared memory or signal its barriers
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * TN));
+  }
+}
+
+typedef CUresult (*encode_fn_t)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                CUtensorMapFloatOOBfill);
+
+encode_fn_t get_encode2() {
+  static encode_fn_t fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (encode_fn_t)p;
+  }
+  return fn;
+}
+
+int make_map2(CUtensorMap* map, const float* ptr, long long rows, long long K, int box_rows) {
+  encode_fn_t enc = get_encode2();
+  if (enc == nullptr) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 4};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+// Same arguments as pcl_gemm_tf32, except that `flags` holds one int per 256-column tile
+// and `gather_ctas` is rounded up to an even number.  Returns cudaErrorNotSupported when the
+// device cannot co-schedule a single pair of CTAs with this much shared memory.
+PCL_API int pcl_gemm_tf32_2sm(const float* A, float* b_stage, float* C, int M, int N, int K,
+                              long long ldc, int epi, const float* bnorm, float* row_min, int* row_arg,
+                              const float* const* b_shards, int* flags, int world, int rank,
+                              int rows_per_shard, int epoch, int gather_ctas, PclStatus* status,
+                              int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K & 3) || ((uintptr_t)A & 15) || ((uintptr_t)b_stage & 15)) return (int)cudaErrorInvalidValue;
+  if (epi == 0 && C == nullptr) return (int)cudaErrorInvalidValue;
+  if (epi == 1 && (bnorm == nullptr || row_min == nullptr || row_arg == nullptr))
+    return (int)cudaErrorInvalidValue;
+  CUtensorMap tmA, tmB;
+  int rc = make_map2(&tmA, A, M, K, HM);
+  if (rc) return rc;
+  rc = make_map2(&tmB, b_stage, N, K, HN);
+  if (rc) return rc;
+  Gemm2Args a;
+  a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.epi = epi;
+  a.bnorm = bnorm; a.row_min = row_min; a.row_arg = row_arg;
+  a.b_shards = b_shards; a.b_stage = b_stage; a.flags = flags;
+  a.world = world; a.rank = rank; a.rows_per_shard = rows_per_shard > 0 ? rows_per_shard : N;
+  a.epoch = epoch; a.status = status;
+  const bool fused = (world > 1 && b_shards != nullptr);
+  a.gather_ctas = fused ? (gather_ctas > 0 ? ((gather_ctas + 1) & ~1) : 16) : 0;
+  if (fused && flags == nullptr) return (int)cudaErrorInvalidValue;
+
+  cudaError_t e = cudaFuncSetAttribute(gemm_tf32_2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       SMEM_BYTES);
+  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // every cluster of the grid must be resident at once: MMA pairs wait for the gather CTAs
+  static int max_clusters = -1;
+  if (max_clusters < 0) {
+    cfg.gridDim = dim3(2, 1, 1);
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_tf32_2sm_kernel, &cfg);
+    if (e != cudaSuccess) return (int)e;
+    max_clusters = n;
+  }
+  int clusters = max_clusters;
+  if (num_sms > 0 && num_sms / 2 < clusters) clusters = num_sms / 2;
+  if (clusters < 1 + a.gather_ctas / 2) return (int)cudaErrorNotSupported;
+  const int m_tiles = (M + TM - 1) / TM;
+  int mma_pairs = clusters - a.gather_ctas / 2;
+  const long long n_items = (epi == 0) ? (long long)m_tiles * ((N + TN - 1) / TN) : (long long)m_tiles;
+  if (mma_pairs > n_items) mma_pairs = (int)n_items;
+  cfg.gridDim = dim3((unsigned)(a.gather_ctas + 2 * mma_pairs), 1, 1);
+  e = cudaLaunchKernelEx(&cfg, gemm_tf32_2sm_kernel, tmA, tmB, a);
+  if (e != cudaSuccess) return (int)e;
+  return pcl_last_error();
+}

@@ -45,6 +45,7 @@ SIGS = {
     "pcl_mf_sgd_pass": "pppqppppppifffiifipipppp",
     "pcl_mf_sse": "pppqppppifppp",
     "pcl_gemm_tf32": "pppiiiqipppppiiiiipip",
+    "pcl_gemm_tf32_2sm": "pppiiiqipppppiiiiipip",
     "pcl_split3_tf32": "ppqiip",
     "pcl_dense_read": "ppqqiipqQpp",
     "pcl_dense_bupdate": "ppqqiiiffpqQppppp",

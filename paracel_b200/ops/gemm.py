@@ -13,6 +13,7 @@ the tensor cores already work on the tiles that have arrived.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -20,6 +21,18 @@ import torch.distributed as dist
 
 from . import _lib
 from ..parallel.symm import SymmBuffer
+
+
+# "2sm": pairs of CTAs on one 256 x 256 tile (tcgen05 cta_group::2, gemm_tf32_2sm.cu);
+# "1sm": one CTA per 128 x 128 tile (gemm_tf32.cu).
+KERNEL = os.environ.get("PCL_GEMM_KERNEL", "2sm")
+
+
+def _entry(kernel: Optional[str] = None) -> str:
+    k = kernel or KERNEL
+    if k not in ("1sm", "2sm"):
+        raise ValueError(f"unknown GEMM kernel {k!r}")
+    return "pcl_gemm_tf32_2sm" if k == "2sm" else "pcl_gemm_tf32"
 
 
 def _pad_k(x: torch.Tensor) -> torch.Tensor:
@@ -39,16 +52,43 @@ def split3(x: torch.Tensor, is_b: bool) -> torch.Tensor:
     return out
 
 
-def _launch(A, B, C, epi, bnorm, row_min, row_arg, status=None):
+_STATUS = {}
+
+
+def _status(device) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    st = _STATUS.get(key)
+    if st is None:
+        st = _STATUS[key] = torch.zeros(4, dtype=torch.int64, device=device)
+    return st
+
+
+def check_status(device=None) -> None:
+    """Raise if a GEMM launched by ``gemm_nt`` / ``argmin_nt`` on ``device`` gave up on a wait
+    (synchronises the device)."""
+    dev = torch.device(device if device is not None else torch.cuda.current_device())
+    st = _STATUS.get(dev.index or 0)
+    if st is None:
+        return
+    host = st.cpu()
+    if int(host[0].item()) & 0xFFFFFFFF:
+        st.zero_()
+        raise RuntimeError(f"GEMM wait timed out: wait id {int(host[1].item()) & 0xFFFFFFFF}, "
+                           f"expected {int(host[2])}, saw {int(host[3])}")
+
+
+def _launch(A, B, C, epi, bnorm, row_min, row_arg, status=None, kernel=None):
     M, K = A.shape
+    if status is None:
+        status = _status(A.device)
     N = B.shape[0]
     ldc = C.stride(0) if C is not None else 0
-    _lib.call("pcl_gemm_tf32", A, B, C, M, N, K, ldc, epi, bnorm, row_min, row_arg, None, None, 1, 0,
+    _lib.call(_entry(kernel), A, B, C, M, N, K, ldc, epi, bnorm, row_min, row_arg, None, None, 1, 0,
               N, 0, 0, status, 0, _lib.stream_ptr())
 
 
 def gemm_nt(A: torch.Tensor, B: torch.Tensor, out: Optional[torch.Tensor] = None,
-            precise: bool = False) -> torch.Tensor:
+            precise: bool = False, kernel: Optional[str] = None) -> torch.Tensor:
     _lib.check_cuda(A, torch.float32, "A")
     _lib.check_cuda(B, torch.float32, "B")
     assert A.shape[1] == B.shape[1]
@@ -59,12 +99,12 @@ def gemm_nt(A: torch.Tensor, B: torch.Tensor, out: Optional[torch.Tensor] = None
         A2, B2 = _pad_k(A), _pad_k(B)
     if out is None:
         out = torch.empty(M, N, device=A.device, dtype=torch.float32)
-    _launch(A2, B2, out, 0, None, None, None)
+    _launch(A2, B2, out, 0, None, None, None, kernel=kernel)
     return out
 
 
 def argmin_nt(A: torch.Tensor, B: torch.Tensor, bnorm: Optional[torch.Tensor] = None,
-              precise: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+              precise: bool = False, kernel: Optional[str] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """(min value of bnorm[n] - 2 a.b_n, its index n) per row of A."""
     _lib.check_cuda(A, torch.float32, "A")
     _lib.check_cuda(B, torch.float32, "B")
@@ -78,7 +118,7 @@ def argmin_nt(A: torch.Tensor, B: torch.Tensor, bnorm: Optional[torch.Tensor] = 
         A2, B2 = _pad_k(A), _pad_k(B)
     row_min = torch.empty(M, device=A.device, dtype=torch.float32)
     row_arg = torch.empty(M, device=A.device, dtype=torch.int32)
-    _launch(A2, B2, None, 1, bnorm, row_min, row_arg)
+    _launch(A2, B2, None, 1, bnorm, row_min, row_arg, kernel=kernel)
     return row_min, row_arg
 
 
@@ -90,7 +130,8 @@ class DenseReadGemm:
     make sure nobody writes the shards while a call is in flight (barrier or SSP clock).
     """
 
-    def __init__(self, N: int, K: int, group=None, device=None, gather_ctas: int = 16):
+    def __init__(self, N: int, K: int, group=None, device=None, gather_ctas: int = 16,
+                 kernel: Optional[str] = None):
         if K % 4:
             raise ValueError("K must be a multiple of 4")
         self.N, self.K = N, K
@@ -106,6 +147,7 @@ class DenseReadGemm:
         self.status = torch.zeros(4, dtype=torch.int64, device=self.device)
         self.epoch = 0
         self.gather_ctas = gather_ctas
+        self.entry = _entry(kernel)
 
     def local_rows(self) -> Tuple[int, int]:
         lo = self.rank * self.rps
@@ -124,13 +166,13 @@ class DenseReadGemm:
         if argmin_bnorm is None:
             if out is None:
                 out = torch.empty(M, self.N, device=A.device, dtype=torch.float32)
-            _lib.call("pcl_gemm_tf32", A, stage, out, M, self.N, self.K, out.stride(0), 0, None, None,
+            _lib.call(self.entry, A, stage, out, M, self.N, self.K, out.stride(0), 0, None, None,
                       None, shards, self.flags, self.world, self.rank, self.rps, self.epoch,
                       self.gather_ctas, self.status, 0, _lib.stream_ptr())
             return out
         row_min = torch.empty(M, device=A.device, dtype=torch.float32)
         row_arg = torch.empty(M, device=A.device, dtype=torch.int32)
-        _lib.call("pcl_gemm_tf32", A, stage, None, M, self.N, self.K, 0, 1, argmin_bnorm, row_min,
+        _lib.call(self.entry, A, stage, None, M, self.N, self.K, 0, 1, argmin_bnorm, row_min,
                   row_arg, shards, self.flags, self.world, self.rank, self.rps, self.epoch,
                   self.gather_ctas, self.status, 0, _lib.stream_ptr())
         return row_min, row_arg

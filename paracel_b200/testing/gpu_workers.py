@@ -132,7 +132,7 @@ def mf_train(comm, server_info, nu, ni, nnz, k, rounds, staleness):
     return {"rmse0": r0, "rmse1": r1, "nnz_local": n_local, "mu": m.mu}
 
 
-def fused_gather_gemm(comm, server_info, N, K, M):
+def fused_gather_gemm(comm, server_info, N, K, M, kernel=None):
     """B is sharded by rows over the ranks; every rank multiplies its own A by the whole B."""
     from paracel_b200.ops.gemm import DenseReadGemm
     rank, world = comm.get_rank(), comm.get_size()
@@ -142,7 +142,7 @@ def fused_gather_gemm(comm, server_info, N, K, M):
     Bfull = torch.randn(N, K, device=dev, generator=g)        # same on every rank
     g.manual_seed(1000 + rank)
     A = torch.randn(M, K, device=dev, generator=g)
-    op = DenseReadGemm(N, K)
+    op = DenseReadGemm(N, K, kernel=kernel)
     lo, hi = op.local_rows()
     op.shard[: hi - lo] = Bfull[lo:hi]
     torch.cuda.synchronize()

@@ -52,9 +52,10 @@ def test_mf_two_ranks_converges_like_one_rank():
 
 
 @needs2
-def test_fused_allgather_gemm_two_ranks():
+@pytest.mark.parametrize("kernel", ["1sm", "2sm"])
+def test_fused_allgather_gemm_two_ranks(kernel):
     from paracel_b200.testing.gpu_workers import fused_gather_gemm
-    res = _job(2).run(fused_gather_gemm, (1000, 64, 900), timeout_s=300)
+    res = _job(2).run(fused_gather_gemm, (1000, 64, 900, kernel), timeout_s=300)
     for r in res:
         assert r["err0"] < 5e-3 and r["err1"] < 5e-3, r
         assert r["argmin_ok"]
