@@ -53,6 +53,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "nccl_torch"])
     ap.add_argument("--steps", type=int, default=0)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-scramble", action="store_true",
+                    help="pagerank: keep the raw R-MAT vertex labels (equal id ranges are then unbalanced)")
     args = ap.parse_args()
     if args.config == "lr_cpu":
         return lr_cpu(args)
@@ -180,6 +182,9 @@ def main():
         for c in range((m_edges + chunk - 1) // chunk):
             mm = min(chunk, m_edges - c * chunk)
             s, d = synth.rmat_edges_chunk(scale_log, mm, 0.57, 0.19, 0.19, seed=500 + c, device=dev)
+            if not args.no_scramble:   # balanced ownership of equal id ranges (labels are arbitrary)
+                s = synth.scramble_vertex_blocks(s, scale_log)
+                d = synth.scramble_vertex_blocks(d, scale_log)
             keep = pr.owner_of(d) == rank
             srcs.append(s[keep].to(torch.int32))
             dsts.append(d[keep].to(torch.int32))

@@ -140,7 +140,7 @@ class LdaNcclTorch(_Base):
         self.n_wk.view(-1).index_add_(0, self.words * self.K + self.z, torch.ones(T, dtype=torch.int32, device=dev))
         if self.world > 1:
             dist.all_reduce(self.n_wk, group=self.group)
-        b = torch.linspace(0, T, self.nbatch + 1).long().tolist()
+        b = [T * i // self.nbatch for i in range(self.nbatch + 1)]
         self.batches = list(zip(b[:-1], b[1:]))
 
     def step(self, chunk=1 << 18):

@@ -59,6 +59,8 @@ SIGS = {
     "pcl_als_solve": "pppppppppppqifip",
     "pcl_kmeans_accumulate": "ppqippp",
     "pcl_topk_rows": "pqiippfippp",
+    "pcl_partition_count": "ppqiipp",
+    "pcl_partition_scatter": "pppqiipqppppip",
     "pcl_gram": "pqipp",
     "pcl_allreduce_sum_f64": "ppipppiiiqQpp",
     "pcl_ssp_commit": "piiqp",

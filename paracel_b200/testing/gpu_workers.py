@@ -325,3 +325,32 @@ def kmeans_allreduce_lda_two_ranks(comm, server_info):
     comm.synchronize()
     lda.free()
     return out
+
+
+def device_exchange_ranks(comm, server_info, pattern):
+    """Every rank parses a different slice of one seeded triple list; after the device exchange
+    each rank must hold exactly the triples that the placement function assigns to it, and the
+    renumbering must agree with the union over its grid row / column."""
+    from paracel_b200.load.device_exchange import DeviceExchange
+    rank, world = comm.get_rank(), comm.get_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev)
+    g.manual_seed(123)
+    n = 100_000
+    A = torch.randint(0, 4000, (n,), device=dev, generator=g)
+    B = torch.randint(0, 3000, (n,), device=dev, generator=g)
+    W = torch.rand(n, device=dev, generator=g)
+    lo, hi = rank * n // world, (rank + 1) * n // world
+    ex = DeviceExchange(pattern)
+    a2, b2, w2 = ex.exchange(A[lo:hi].contiguous(), B[lo:hi].contiguous(), W[lo:hi].contiguous())
+    own = ex.owner(A, B) == rank
+    key = lambda a, b, w: torch.sort(a.double() * 1e7 + b.double() * 1e3 + w.double()).values
+    ok_triples = bool(torch.allclose(key(a2, b2, w2), key(A[own], B[own], W[own])))
+    ri, ci, rm, cm = ex.index_mapping(a2, b2)
+    rowc, colc = rank // ex.npy, rank % ex.npy
+    all_owner = ex.owner(A, B)
+    in_row = (all_owner // ex.npy) == rowc
+    in_col = (all_owner % ex.npy) == colc
+    ok_maps = bool(torch.equal(rm, torch.unique(A[in_row])) and torch.equal(cm, torch.unique(B[in_col])))
+    ok_idx = bool(torch.equal(rm[ri], a2) and torch.equal(cm[ci], b2))
+    return {"triples": ok_triples, "maps": ok_maps, "idx": ok_idx, "n": int(a2.numel())}

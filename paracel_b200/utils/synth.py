@@ -113,6 +113,21 @@ def lda_corpus_chunk(n_docs: int, vocab: int, s: float, mean_len: float, seed: i
     return ptr, words
 
 
+def scramble_vertex_blocks(v: torch.Tensor, scale: int, block_log: int = 10) -> torch.Tensor:
+    """Bijection on [0, 2^scale) that keeps blocks of 2^block_log consecutive ids together and
+    moves block b to (b * odd constant) mod 2^(scale - block_log).  R-MAT skews every id bit the
+    same way, so equal id ranges carry very unequal edge counts; after this relabelling the top
+    bits depend on all bits of the block number and equal ranges are balanced, while the
+    locality inside a block (4 KB of an fp32 vector) is unchanged."""
+    if scale <= block_log:
+        return v
+    hb = scale - block_log
+    blk = v >> block_log
+    off = v & ((1 << block_log) - 1)
+    nb = (blk * 0x9E3779B1) & ((1 << hb) - 1)
+    return (nb << block_log) | off
+
+
 def rmat_edges_chunk(scale: int, m: int, a: float, b: float, c: float, seed: int, device):
     """``m`` edges of an R-MAT graph with 2^scale vertices (quadrant probabilities a, b, c,
     1-a-b-c): (src, dst) int64."""

@@ -81,3 +81,13 @@ def test_kmeans_allreduce_lda_two_ranks():
         assert r["allreduce"] and r["kmeans"], r
         assert r["lda_counts"][0] == r["lda_counts"][2] == r["lda_counts"][1], r
         assert r["lda_ll_up"] and r["lda_consistent"], r
+
+
+@needs2
+@pytest.mark.parametrize("pattern", ["fmap", "fsmap"])
+def test_device_loader_exchange_two_ranks(pattern):
+    from paracel_b200.testing.gpu_workers import device_exchange_ranks
+    res = _job(2).run(device_exchange_ranks, (pattern,), timeout_s=300)
+    assert sum(r["n"] for r in res) == 100_000
+    for r in res:
+        assert r["triples"] and r["maps"] and r["idx"], r
