@@ -48,6 +48,42 @@ class bag_type(Generic[T]):
         return self
 
 
+# (row id, column id, weight) as produced by the loader; the "compact" form has dense int ids
+triple_type = tuple
+compact_triple_type = tuple
+threads_num = THREADS_NUM
+
+
+def is_comm_builtin(v) -> bool:
+    """Scalars that travel as one fixed-size element (paracel_types.hpp:63-118)."""
+    return isinstance(v, (bool, int, float))
+
+
+def is_comm_container(v) -> bool:
+    """Flat containers of builtin scalars (or a string) that travel as size + payload."""
+    if isinstance(v, (str, bytes)):
+        return True
+    try:
+        import numpy as np
+        if isinstance(v, np.ndarray):
+            return v.ndim == 1
+    except ImportError:  # pragma: no cover
+        pass
+    return isinstance(v, (list, tuple)) and all(is_comm_builtin(x) for x in v)
+
+
+def is_matrix(v) -> bool:
+    """Dense 2-D arrays and scipy sparse matrices."""
+    try:
+        import numpy as np
+        if isinstance(v, np.ndarray):
+            return v.ndim == 2
+        import scipy.sparse as sp
+        return bool(sp.issparse(v))
+    except ImportError:  # pragma: no cover
+        return False
+
+
 def is_atomic(v) -> bool:
     return isinstance(v, (bool, int, float, str))
 

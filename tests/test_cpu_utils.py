@@ -248,3 +248,37 @@ def test_misc(tmp_path):
     p.write_text("".join(f"{i}\n" for i in range(10)))
     assert tail(str(p), 3, int) == [7, 8, 9]
     assert tail(str(p), 20) == [str(i) for i in range(10)]
+
+
+def test_hash_module_matches_the_native_functions():
+    from paracel_b200._core import core
+    from paracel_b200.utils.hash import hash_combine, hash_value
+    c = core()
+    assert hash_value(42) == 42                        # std::hash of an integer is the identity
+    assert hash_value("abc") == c.hash_string("abc")
+    assert hash_value(["a", "b"]) == c.hash_string("vechashab")
+    assert hash_value(("a", 7)) == hash_combine(c.hash_string("a"), 7)
+    assert hash_value(("a", 7)) != hash_value((7, "a"))
+
+
+def test_type_traits_and_small_helpers():
+    import numpy as np
+    from paracel_b200.utils import misc, types
+    assert types.is_comm_builtin(3) and not types.is_comm_builtin([3])
+    assert types.is_comm_container([1, 2.0]) and types.is_comm_container("x")
+    assert types.is_matrix(np.zeros((2, 3))) and not types.is_matrix(np.zeros(3))
+    assert types.threads_num == 5
+    m = np.arange(6, dtype=float).reshape(2, 3)
+    flat = misc.mat2vec(m)
+    assert flat == [0.0, 3.0, 1.0, 4.0, 2.0, 5.0]      # column major
+    assert np.array_equal(misc.vec2mat(flat, 2), m)
+    assert misc.evec2vec(misc.vec2evec([1, 2])) == [1.0, 2.0]
+    assert misc.ring_bsearch([10, 20, 30], 15) == 1 and misc.ring_bsearch([10, 20, 30], 35) == 0
+    import heapq
+    h = [misc.heap_node("a", 3.0), misc.heap_node("b", 1.0), misc.heap_node("c", 2.0)]
+    heapq.heapify(h)
+    assert heapq.heappop(h).key == "b"
+    ports = misc.get_ports(2)
+    assert len(ports) == 2 and all(2014 <= p < 65535 for p in ports)
+    with __import__("pytest").raises(RuntimeError):
+        misc.ERROR_ABORT("boom")
