@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--staleness", type=int, default=2)
     ap.add_argument("--seed", type=int, default=20240611)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--phases", action="store_true",
+                    help="after the timed steps run two extra rounds with per-phase device timing")
     ap.add_argument("--no-balance", action="store_true")
     ap.add_argument("--hot-mix", type=float, default=1.0)
     ap.add_argument("--sgd-blocks", type=int, default=0)
@@ -169,6 +171,15 @@ def main():
     model.clock.check()
     run_rmse = model.running_rmse()
     value = args.nnz * K / (ms * 1e-3)
+    phases = None
+    if args.phases and hasattr(model, "phase_times_ms"):   # extra untimed rounds, diagnostics only
+        barrier()
+        model.phase_timing = True
+        for _ in range(2):
+            model.round()
+        phases = model.phase_times_ms()
+        model.phase_timing = False
+        barrier()
 
     # ---- end to end: ratings streamed from pinned host memory each round
     e2e = None
@@ -184,6 +195,8 @@ def main():
                "h2d_bytes_per_step": int(model.h2d_bytes), "d2h_bytes_per_step": 8}
     final_rmse = model.running_rmse()
 
+    factor_mb = ((model.lu.numel() + model.li.numel()) * getattr(model, "D", args.rank) * 4 / 1e6
+                 if hasattr(model, "lu") and hasattr(model, "li") else (args.users + args.items) * args.rank * 4 / 1e6 / world)
     mx = torch.tensor([local_nnz], dtype=torch.int64, device=dev)
     mn = mx.clone()
     if world > 1:
@@ -210,14 +223,15 @@ def main():
                 "global_batch": args.nnz, "seq_len": None,
                 "lr": args.alpha, "l2": args.beta, "ssp_staleness": args.staleness,
                 "parallelism": "ps-shards-in-hbm x fsmap %dx%d" % (model.npx, model.npy),
-                "l2_policy": "inputs larger than L2: %.0f MB of ratings per rank and %.0f MB of "
-                             "factor rows are streamed every step"
-                             % (local_nnz * 12 / 1e6, (args.users + args.items) * model.D * 4 / 1e6 / world),
+                "l2_policy": "inputs larger than L2 (126 MB): per rank %.0f MB of ratings are streamed and "
+                             "%.0f MB of factor rows are read and updated every step"
+                             % (local_nnz * 4.4 / 1e6, factor_mb),
                 "ratings_per_rank_max": int(mx.item()), "ratings_per_rank_min": int(mn.item()),
             },
             "clocks": clocks,
             "e2e": e2e,
             "gpu_launches": launches,
+            "phases_ms": phases,
             "running_rmse_device_phase": run_rmse,
             "running_rmse_final": final_rmse,
             "setup_s": t_setup,

@@ -42,13 +42,16 @@ def _pad_rank(k: int) -> int:
 def balanced_groups(counts: torch.Tensor, ngroups: int) -> torch.Tensor:
     """Assign ids to ``ngroups`` groups with near-equal total count.
 
-    The ``heavy`` ids (count above 1/(64*ngroups) of the total) are placed
-    greedily, largest first, on the lightest group; the light tail is dealt
-    round-robin, which is balanced in expectation.  Returns an int32 group id
-    per id.  With ``ngroups == 1`` everything is group 0.
+    The ``heavy`` ids (count above 1/(64*ngroups) of the total) are placed greedily, largest
+    first, on the lightest group.  The light tail then fills every group up to the common
+    target: a tail id goes to group g with a share proportional to the group's remaining
+    deficit, spread evenly over the popularity ranks by a golden-ratio sequence (so a group
+    that already holds a very popular id receives few tail ids instead of an equal part).
+    Returns an int32 group id per id.  With ``ngroups == 1`` everything is group 0.
     """
     n = counts.numel()
-    grp = (torch.arange(n, device=counts.device, dtype=torch.int64) % ngroups).to(torch.int32)
+    dev = counts.device
+    grp = (torch.arange(n, device=dev, dtype=torch.int64) % ngroups).to(torch.int32)
     if ngroups == 1:
         return grp
     total = float(counts.sum().item())
@@ -59,19 +62,23 @@ def balanced_groups(counts: torch.Tensor, ngroups: int) -> torch.Tensor:
     hc = counts[heavy].to(torch.float64)
     order = torch.argsort(hc, descending=True)
     heavy, hc = heavy[order].cpu(), hc[order].cpu()
-    light_mask = torch.ones(n, dtype=torch.bool, device=counts.device)
-    light_mask[heavy.to(counts.device)] = False
     load = torch.zeros(ngroups, dtype=torch.float64)
-    # tail contribution per group (round robin over ids)
-    tail = torch.zeros(ngroups, dtype=torch.float64, device=counts.device)
-    tail.index_add_(0, grp[light_mask].to(torch.int64), counts[light_mask].to(torch.float64))
-    load += tail.cpu()
     g_heavy = torch.empty(heavy.numel(), dtype=torch.int32)
     for j in range(heavy.numel()):
         g = int(torch.argmin(load))
         g_heavy[j] = g
         load[g] += hc[j]
-    grp[heavy.to(counts.device)] = g_heavy.to(counts.device)
+    light_mask = torch.ones(n, dtype=torch.bool, device=dev)
+    light_mask[heavy.to(dev)] = False
+    light = torch.nonzero(light_mask).flatten()
+    deficit = torch.clamp(total / ngroups - load, min=0.0)
+    if float(deficit.sum()) <= 0.0:
+        deficit = torch.ones(ngroups, dtype=torch.float64)
+    edges = (torch.cumsum(deficit, 0) / deficit.sum()).to(dev)
+    edges[-1] = 1.0
+    x = torch.frac(torch.arange(light.numel(), device=dev, dtype=torch.float64) * 0.6180339887498949)
+    grp[light] = torch.clamp(torch.searchsorted(edges, x, right=True), max=ngroups - 1).to(torch.int32)
+    grp[heavy.to(dev)] = g_heavy.to(dev)
     return grp
 
 
@@ -117,6 +124,9 @@ class MfSgdGpu:
         self.host_stream = None
         self.h2d_bytes = 0
         self._loaded = False
+        # optional per-phase device timing of round() (diagnostics; adds event records only)
+        self.phase_timing = False
+        self._phase_events = []
 
     # ------------------------------------------------------------------ data
     def owner_of(self, ugrp: torch.Tensor, igrp: torch.Tensor) -> torch.Tensor:
@@ -390,18 +400,45 @@ class MfSgdGpu:
             return True
         return (c - self._pulled_at) >= self.staleness
 
+    def _mark(self):
+        if self.phase_timing:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self._phase_events.append(e)
+
     def round(self):
+        self._mark()
         if self.need_pull():
             self.pull()
             self._pulled_at = self.clock.clock
         elif self.world > 1:
             self.clock.wait()  # keep the staleness bound while serving from the cache
+        self._mark()
         self.sse.zero_()
         self.sgd_pass()
+        self._mark()
         self.push()
         if not self.ssp and self.world > 1:
             self._barrier()
         self.clock.commit()
+        self._mark()
+
+    def phase_times_ms(self):
+        """Mean device time of the pull-or-wait / SGD / push+commit phases over the rounds run
+        since ``phase_timing`` was switched on (synchronises)."""
+        torch.cuda.synchronize(self.device)
+        ev = self._phase_events
+        n = len(ev) // 4
+        out = {"pull_or_wait": 0.0, "sgd": 0.0, "push_commit": 0.0, "rounds": n}
+        for r in range(n):
+            a, b, c, d = ev[4 * r: 4 * r + 4]
+            out["pull_or_wait"] += a.elapsed_time(b)
+            out["sgd"] += b.elapsed_time(c)
+            out["push_commit"] += c.elapsed_time(d)
+        for k in ("pull_or_wait", "sgd", "push_commit"):
+            out[k] = out[k] / max(n, 1)
+        self._phase_events = []
+        return out
 
     def fit(self):
         for _ in range(self.rounds):
