@@ -53,7 +53,8 @@ def parse_args():
     ap.add_argument("--hot-mix", type=float, default=1.0)
     ap.add_argument("--sgd-blocks", type=int, default=0)
     ap.add_argument("--hot-rows", type=int, default=106)
-    ap.add_argument("--variant", type=int, default=0, help="2: experimental 8-lanes-per-rating SGD kernel")
+    ap.add_argument("--variant", type=int, default=0, help="SGD kernel: 0 automatic (16 lanes per rating at rank 128), 1: 32 lanes per rating, "
+                         "2: experimental 8 lanes per rating, 3: 16 lanes per rating")
     ap.add_argument("--chunks-per-flush", type=int, default=8)
     ap.add_argument("--zipf-s", type=float, default=1.1)
     return ap.parse_args()

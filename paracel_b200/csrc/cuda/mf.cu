@@ -94,10 +94,13 @@ __global__ void __launch_bounds__(512, 2) mf_sgd_kernel(MfArgs a) {
   constexpr int D = VEC * 32;
   extern __shared__ float smem[];
   const int T = a.hot_T;
-  float* hv = smem;                    // T x D
-  float* hbase = hv + (size_t)T * D;   // T x D
-  float* hb = hbase + (size_t)T * D;   // T
-  float* hbb = hb + T;                 // T
+  // value at the start of the mixing period (float) + fixed-point delta of the period (2^-22
+  // units, integer shared-memory atomics: native, no retry loop under contention)
+  int* hd = reinterpret_cast<int*>(smem);                     // T x D
+  float* hbase = smem + (size_t)T * D;                        // T x D
+  int* hbd = reinterpret_cast<int*>(hbase + (size_t)T * D);   // T
+  float* hbb = reinterpret_cast<float*>(hbd + T);             // T
+  constexpr float FX = 4194304.f, FXI = 1.f / 4194304.f;
   const int lane = threadIdx.x & 31;
   const int wic = threadIdx.x >> 5;
   const int wpc = blockDim.x >> 5;
@@ -118,21 +121,19 @@ __global__ void __launch_bounds__(512, 2) mf_sgd_kernel(MfArgs a) {
         const int sidx = row * D + (e % VEC) * 32 + (e / VEC);
         float* gp = a.H + (size_t)row * D + e;
         if (it > 0) {
-          const float d = hv[sidx] - hbase[sidx];
-          if (d != 0.f) atomicAdd(gp, d * a.flush_scale);
+          const int d = hd[sidx];
+          if (d != 0) atomicAdd(gp, (float)d * (FXI * a.flush_scale));
         }
-        const float v = __ldcg(gp);
-        hv[sidx] = v;
-        hbase[sidx] = v;
+        hd[sidx] = 0;
+        hbase[sidx] = __ldcg(gp);
       }
       for (int row = threadIdx.x; row < T; row += blockDim.x) {
         if (it > 0) {
-          const float d = hb[row] - hbb[row];
-          if (d != 0.f) atomicAdd(a.bi + row, d * a.flush_scale);
+          const int d = hbd[row];
+          if (d != 0) atomicAdd(a.bi + row, (float)d * (FXI * a.flush_scale));
         }
-        const float v = __ldcg(a.bi + row);
-        hb[row] = v;
-        hbb[row] = v;
+        hbd[row] = 0;
+        hbb[row] = __ldcg(a.bi + row);
       }
       __syncthreads();
     }
@@ -193,8 +194,9 @@ __global__ void __launch_bounds__(512, 2) mf_sgd_kernel(MfArgs a) {
       if (u < 0) continue;  // padding entry (warp-uniform)
       if (hot) {
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) h.v[k] = hv[i * D + k * 32 + lane];
-        bi = hb[i];
+        for (int k = 0; k < VEC; ++k)
+          h.v[k] = fmaf((float)hd[i * D + k * 32 + lane], FXI, hbase[i * D + k * 32 + lane]);
+        bi = fmaf((float)hbd[i], FXI, hbb[i]);
       }
       if (u != cur_u) {
         if (cur_u >= 0) {
@@ -231,8 +233,8 @@ __global__ void __launch_bounds__(512, 2) mf_sgd_kernel(MfArgs a) {
       bu += a2e - ab * bu;
       if (hot) {
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) atomicAdd(&hv[i * D + k * 32 + lane], dh.v[k]);
-        if (lane == 0) atomicAdd(&hb[i], dbi);
+        for (int k = 0; k < VEC; ++k) atomicAdd(&hd[i * D + k * 32 + lane], __float2int_rn(dh.v[k] * FX));
+        if (lane == 0) atomicAdd(&hbd[i], __float2int_rn(dbi * FX));
       } else {
         red_row<VEC>(a.H + (long long)i * D + lane * VEC, dh);
         if (lane == 0) atomicAdd(a.bi + i, dbi);
@@ -256,12 +258,12 @@ __global__ void __launch_bounds__(512, 2) mf_sgd_kernel(MfArgs a) {
     for (int idx = threadIdx.x; idx < T * D; idx += blockDim.x) {
       const int row = idx / D, e = idx % D;
       const int sidx = row * D + (e % VEC) * 32 + (e / VEC);
-      const float d = hv[sidx] - hbase[sidx];
-      if (d != 0.f) atomicAdd(a.H + (size_t)row * D + e, d * a.flush_scale);
+      const int d = hd[sidx];
+      if (d != 0) atomicAdd(a.H + (size_t)row * D + e, (float)d * (FXI * a.flush_scale));
     }
     for (int row = threadIdx.x; row < T; row += blockDim.x) {
-      const float d = hb[row] - hbb[row];
-      if (d != 0.f) atomicAdd(a.bi + row, d * a.flush_scale);
+      const int d = hbd[row];
+      if (d != 0) atomicAdd(a.bi + row, (float)d * (FXI * a.flush_scale));
     }
   }
   if (a.sse != nullptr && lane == 0 && sse != 0.f) atomicAdd(a.sse, (double)sse);

@@ -1,0 +1,338 @@
+// MF-SGD pass, rank 128, sixteen lanes per rating: a warp advances TWO chunks of 32
+// ratings at once, one per half-warp, and a lane keeps 8 floats of every 128-float row
+// (elements h*64 + l*4 + t, h < 2, t < 4: two 128-bit loads, each covering 256 contiguous
+// bytes per half-warp).  One warp-wide instruction therefore serves two ratings, which
+// roughly halves the instructions per rating of the 32-lanes-per-rating kernel in mf.cu
+// (that kernel is bound by instruction issue, not by memory).  Everything else is the same
+// algorithm (alg/recommendation/matrix_factorization/mf.hpp:266-280 for the update rule,
+// 217-262 for the mixing weights): user row in registers while the chunk stays on one user,
+// cold item rows read with L1-bypassing loads and updated with vector reductions, the
+// hottest item rows replicated in shared memory per CTA and mixed into the global rows
+// every `cpw` chunks, compact or plain rating stream.
+//
+// Hot replicas are kept as a float base value plus a 32-bit fixed-point delta (2^-22 units):
+// the deltas are accumulated with native integer shared-memory atomics, which neither spin nor
+// retry under contention the way a floating-point shared-memory atomic add does.
+#include "common.cuh"
+
+namespace {
+
+struct MfH16Args {
+  const int* ru;
+  const int* ri;
+  const float* rr;
+  long long nnz;
+  float* W;
+  float* H;
+  float* bu;
+  float* bi;
+  const float* su;
+  const float* si;
+  float mu, alpha, beta;
+  long long nchunks;
+  double* sse;
+  int hot_T;
+  int cpw;
+  float flush_scale;
+  const unsigned int* packed;
+  const int* chdr;
+  const float* rtable;
+};
+
+struct Row8 {
+  float4 a, b;   // elements l*4 .. l*4+3 and 64 + l*4 .. 64 + l*4 + 3
+};
+
+__device__ __forceinline__ Row8 load_cg(const float* row, int l) {
+  Row8 r;
+  r.a = pcl_ldcg4(row + l * 4);
+  r.b = pcl_ldcg4(row + 64 + l * 4);
+  return r;
+}
+
+constexpr float FX_SCALE = 4194304.f;          // 2^22
+constexpr float FX_INV = 1.f / 4194304.f;
+
+// current value of a hot row: base + fixed-point delta
+__device__ __forceinline__ Row8 load_hot(const float* base_row, const int* delta_row, int l) {
+  const float4 b0 = *reinterpret_cast<const float4*>(base_row + l * 4);
+  const float4 b1 = *reinterpret_cast<const float4*>(base_row + 64 + l * 4);
+  const int4 d0 = *reinterpret_cast<const int4*>(delta_row + l * 4);
+  const int4 d1 = *reinterpret_cast<const int4*>(delta_row + 64 + l * 4);
+  Row8 r;
+  r.a.x = fmaf((float)d0.x, FX_INV, b0.x); r.a.y = fmaf((float)d0.y, FX_INV, b0.y);
+  r.a.z = fmaf((float)d0.z, FX_INV, b0.z); r.a.w = fmaf((float)d0.w, FX_INV, b0.w);
+  r.b.x = fmaf((float)d1.x, FX_INV, b1.x); r.b.y = fmaf((float)d1.y, FX_INV, b1.y);
+  r.b.z = fmaf((float)d1.z, FX_INV, b1.z); r.b.w = fmaf((float)d1.w, FX_INV, b1.w);
+  return r;
+}
+
+__device__ __forceinline__ void red_global(float* row, int l, const Row8& d) {
+  pcl_red_add4(row + l * 4, d.a);
+  pcl_red_add4(row + 64 + l * 4, d.b);
+}
+
+__device__ __forceinline__ int to_fx(float x) { return __float2int_rn(x * FX_SCALE); }
+
+__device__ __forceinline__ void add_hot(int* row, int l, const Row8& d) {
+  int* p = row + l * 4;
+  atomicAdd(p, to_fx(d.a.x)); atomicAdd(p + 1, to_fx(d.a.y));
+  atomicAdd(p + 2, to_fx(d.a.z)); atomicAdd(p + 3, to_fx(d.a.w));
+  p += 64;
+  atomicAdd(p, to_fx(d.b.x)); atomicAdd(p + 1, to_fx(d.b.y));
+  atomicAdd(p + 2, to_fx(d.b.z)); atomicAdd(p + 3, to_fx(d.b.w));
+}
+
+__device__ __forceinline__ float dot8(const Row8& x, const Row8& y) {
+  float s = x.a.x * y.a.x;
+  s = fmaf(x.a.y, y.a.y, s); s = fmaf(x.a.z, y.a.z, s); s = fmaf(x.a.w, y.a.w, s);
+  s = fmaf(x.b.x, y.b.x, s); s = fmaf(x.b.y, y.b.y, s); s = fmaf(x.b.z, y.b.z, s);
+  s = fmaf(x.b.w, y.b.w, s);
+  return s;
+}
+
+// out = p * x + q * y, element-wise
+__device__ __forceinline__ Row8 axpby(float p, const Row8& x, float q, const Row8& y) {
+  Row8 o;
+  o.a.x = fmaf(p, x.a.x, q * y.a.x); o.a.y = fmaf(p, x.a.y, q * y.a.y);
+  o.a.z = fmaf(p, x.a.z, q * y.a.z); o.a.w = fmaf(p, x.a.w, q * y.a.w);
+  o.b.x = fmaf(p, x.b.x, q * y.b.x); o.b.y = fmaf(p, x.b.y, q * y.b.y);
+  o.b.z = fmaf(p, x.b.z, q * y.b.z); o.b.w = fmaf(p, x.b.w, q * y.b.w);
+  return o;
+}
+
+__device__ __forceinline__ void add_to(Row8& x, const Row8& d) {
+  x.a.x += d.a.x; x.a.y += d.a.y; x.a.z += d.a.z; x.a.w += d.a.w;
+  x.b.x += d.b.x; x.b.y += d.b.y; x.b.z += d.b.z; x.b.w += d.b.w;
+}
+
+__device__ __forceinline__ Row8 scaled_diff(float s, const Row8& x, const Row8& y) {
+  Row8 o;
+  o.a.x = s * (x.a.x - y.a.x); o.a.y = s * (x.a.y - y.a.y); o.a.z = s * (x.a.z - y.a.z);
+  o.a.w = s * (x.a.w - y.a.w);
+  o.b.x = s * (x.b.x - y.b.x); o.b.y = s * (x.b.y - y.b.y); o.b.z = s * (x.b.z - y.b.z);
+  o.b.w = s * (x.b.w - y.b.w);
+  return o;
+}
+
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
+  constexpr int D = 128;
+  extern __shared__ float smem[];
+  const int T = a.hot_T;
+  int* hd = reinterpret_cast<int*>(smem);                   // T x 128 fixed-point deltas of the period
+  float* hbase = smem + (size_t)T * D;                      // T x 128 values at the start of the period
+  int* hbd = reinterpret_cast<int*>(hbase + (size_t)T * D); // T bias deltas
+  float* hbb = reinterpret_cast<float*>(hbd + T);           // T bias bases
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 4;             // half-warp
+  const int l = lane & 15;
+  // the two half-warps take different branches (padding, user switch, hot or cold item), so every
+  // shuffle names only the 16 lanes of its own half
+  const unsigned gmask = 0xffffu << (16 * g);
+  const int gic = (threadIdx.x >> 5) * 2 + g;   // half-warp index within the CTA
+  const int gpc = (blockDim.x >> 5) * 2;
+  const float ab = a.alpha * a.beta;
+  const float keep = 1.f - ab;
+  float sse = 0.f;
+
+  const long long cta_chunks = a.nchunks > blockIdx.x
+      ? (a.nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const long long iters = (cta_chunks + gpc - 1) / gpc;
+
+  for (long long it = 0; it < iters; ++it) {
+    if (T > 0 && (it % a.cpw) == 0) {
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < T * D; idx += blockDim.x) {
+        float* gp = a.H + idx;           // hot rows are the first T rows of H
+        if (it > 0) {
+          const int d = hd[idx];
+          if (d != 0) atomicAdd(gp, (float)d * (FX_INV * a.flush_scale));
+        }
+        hd[idx] = 0;
+        hbase[idx] = __ldcg(gp);
+      }
+      for (int row = threadIdx.x; row < T; row += blockDim.x) {
+        if (it > 0) {
+          const int d = hbd[row];
+          if (d != 0) atomicAdd(a.bi + row, (float)d * (FX_INV * a.flush_scale));
+        }
+        hbd[row] = 0;
+        hbb[row] = __ldcg(a.bi + row);
+      }
+      __syncthreads();
+    }
+    const long long c = (long long)blockIdx.x + ((long long)gic + it * gpc) * gridDim.x;
+    const bool live = c < a.nchunks;     // uniform per half-warp; a dead half sees only padding
+    const long long base = c * 32;
+    // entries l and l + 16 of this half-warp's chunk
+    int u0 = -1, u1 = -1, i0 = 0, i1 = 0;
+    float r0 = 0.f, r1 = 0.f;
+    if (live) {
+      if (a.packed != nullptr) {
+        const unsigned int pk0 = __ldg(a.packed + base + l);
+        const unsigned int pk1 = __ldg(a.packed + base + 16 + l);
+        const int u_base = __ldg(a.chdr + 3 * c);
+        const unsigned int inc = (unsigned int)__ldg(a.chdr + 3 * c + 1);
+        const int n_valid = __ldg(a.chdr + 3 * c + 2);
+        i0 = (int)(pk0 & 0xffffffu);
+        i1 = (int)(pk1 & 0xffffffu);
+        r0 = __ldg(a.rtable + (pk0 >> 24));
+        r1 = __ldg(a.rtable + (pk1 >> 24));
+        u0 = l < n_valid ? u_base + __popc(inc & (0xffffffffu >> (31 - l))) : -1;
+        u1 = l + 16 < n_valid ? u_base + __popc(inc & (0xffffffffu >> (15 - l))) : -1;
+      } else {
+        u0 = __ldg(a.ru + base + l);       u1 = __ldg(a.ru + base + 16 + l);
+        i0 = __ldg(a.ri + base + l);       i1 = __ldg(a.ri + base + 16 + l);
+        r0 = __ldg(a.rr + base + l);       r1 = __ldg(a.rr + base + 16 + l);
+      }
+    }
+    int cur_u = -1;
+    Row8 w, w0;
+    w.a = w.b = w0.a = w0.b = make_float4(0.f, 0.f, 0.f, 0.f);
+    float bu = 0.f, bu0 = 0.f, s_u = 1.f;
+
+    const int src0 = g << 4;   // first lane of this half-warp
+    int i_nxt = __shfl_sync(gmask, i0, src0);
+    float si_nxt = __ldg(a.si + i_nxt);
+    Row8 h_nxt;
+    h_nxt.a = h_nxt.b = make_float4(0.f, 0.f, 0.f, 0.f);
+    float bi_nxt = 0.f;
+    if (i_nxt >= T) {
+      h_nxt = load_cg(a.H + (long long)i_nxt * D, l);
+      bi_nxt = __ldcg(a.bi + i_nxt);
+    }
+
+#pragma unroll 1
+    for (int j = 0; j < 32; ++j) {
+      const int src = src0 + (j & 15);
+      const int u = __shfl_sync(gmask, j < 16 ? u0 : u1, src);
+      const float r = __shfl_sync(gmask, j < 16 ? r0 : r1, src);
+      const int i = i_nxt;
+      const bool hot = i < T;
+      Row8 h = h_nxt;
+      float bi = bi_nxt;
+      const float s_i = si_nxt;
+      const bool more = j + 1 < 32;
+      if (more) {
+        const int srcn = src0 + ((j + 1) & 15);
+        i_nxt = __shfl_sync(gmask, j + 1 < 16 ? i0 : i1, srcn);
+        si_nxt = __ldg(a.si + i_nxt);
+        if (i_nxt >= T) {
+          h_nxt = load_cg(a.H + (long long)i_nxt * D, l);
+          bi_nxt = __ldcg(a.bi + i_nxt);
+        }
+      }
+      if (u < 0) continue;   // padding (uniform per half-warp)
+      if (hot) {
+        h = load_hot(hbase + i * D, hd + i * D, l);
+        bi = fmaf((float)hbd[i], FX_INV, hbb[i]);
+      }
+      if (u != cur_u) {
+        if (cur_u >= 0) {
+          red_global(a.W + (long long)cur_u * D, l, scaled_diff(s_u, w, w0));
+          if (l == 0) atomicAdd(a.bu + cur_u, s_u * (bu - bu0));
+        }
+        cur_u = u;
+        w = load_cg(a.W + (long long)u * D, l);
+        w0 = w;
+        bu = __ldcg(a.bu + u);
+        bu0 = bu;
+        s_u = __ldg(a.su + u);
+      }
+      float dot = dot8(w, h);
+      dot += __shfl_xor_sync(gmask, dot, 8);
+      dot += __shfl_xor_sync(gmask, dot, 4);
+      dot += __shfl_xor_sync(gmask, dot, 2);
+      dot += __shfl_xor_sync(gmask, dot, 1);
+      float pred = a.mu + bu + bi + dot;
+      pred = fminf(5.f, fmaxf(1.f, pred));
+      const float e = r - pred;
+      sse = fmaf(e, e, sse);
+      const float a2e = 2.f * a.alpha * e;
+      // dH = s_i (a2e W - ab H), W <- (1 - ab) W + a2e H   (both from the pre-update values)
+      const Row8 dh = axpby(s_i * a2e, w, -s_i * ab, h);
+      w = axpby(keep, w, a2e, h);
+      const float dbi = s_i * (a2e - ab * bi);
+      bu += a2e - ab * bu;
+      if (hot) {
+        add_hot(hd + i * D, l, dh);
+        if (l == 0) atomicAdd(&hbd[i], to_fx(dbi));
+      } else {
+        red_global(a.H + (long long)i * D, l, dh);
+        if (l == 0) atomicAdd(a.bi + i, dbi);
+        if (more && i_nxt == i) {   // the prefetched copy predates this update
+          add_to(h_nxt, dh);
+          bi_nxt += dbi;
+        }
+      }
+    }
+    if (cur_u >= 0) {
+      red_global(a.W + (long long)cur_u * D, l, scaled_diff(s_u, w, w0));
+      if (l == 0) atomicAdd(a.bu + cur_u, s_u * (bu - bu0));
+    }
+  }
+  if (T > 0) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < T * D; idx += blockDim.x) {
+      const int d = hd[idx];
+      if (d != 0) atomicAdd(a.H + idx, (float)d * (FX_INV * a.flush_scale));
+    }
+    for (int row = threadIdx.x; row < T; row += blockDim.x) {
+      const int d = hbd[row];
+      if (d != 0) atomicAdd(a.bi + row, (float)d * (FX_INV * a.flush_scale));
+    }
+  }
+  if (a.sse != nullptr && l == 0 && sse != 0.f) atomicAdd(a.sse, (double)sse);
+}
+
+}  // namespace
+
+// Same contract as pcl_mf_sgd_pass (mf.cu) for D = 128: user-major sorted ratings in chunks of
+// 32, plain (ru, ri, rr) or compact (packed, chdr, rtable) stream, hot item rows (local index
+// below hot_T) replicated in shared memory and mixed every `cpw` chunks per half-warp with
+// weight `flush_scale` (<= 0: 1 / blocks).  `blocks` <= 0 selects one CTA per SM; `threads` is 512, 640 (default), 768 or 1024
+// (threads / 16 chunks in flight per CTA).
+PCL_API int pcl_mf_sgd_pass_h16(const int* ru, const int* ri, const float* rr, long long nnz,
+                                float* W, float* H, float* bu, float* bi, const float* su,
+                                const float* si, float mu, float alpha, float beta, int hot_T,
+                                int cpw, float flush_scale, int blocks, double* sse,
+                                const unsigned int* packed, const int* chdr, const float* rtable,
+                                int threads, cudaStream_t stream) {
+  if (nnz <= 0) return 0;
+  if (nnz % 32 != 0 || hot_T < 0) return (int)cudaErrorInvalidValue;
+  if (packed != nullptr && (chdr == nullptr || rtable == nullptr)) return (int)cudaErrorInvalidValue;
+  if (packed == nullptr && (ru == nullptr || ri == nullptr || rr == nullptr))
+    return (int)cudaErrorInvalidValue;
+  MfH16Args a;
+  a.ru = ru; a.ri = ri; a.rr = rr; a.nnz = nnz;
+  a.W = W; a.H = H; a.bu = bu; a.bi = bi; a.su = su; a.si = si;
+  a.mu = mu; a.alpha = alpha; a.beta = beta;
+  a.nchunks = nnz / 32;
+  a.sse = sse;
+  a.hot_T = hot_T;
+  a.cpw = cpw > 0 ? cpw : 8;
+  a.packed = packed; a.chdr = chdr; a.rtable = rtable;
+  if (threads <= 0) threads = 640;   // 20 warps = 40 chunks in flight per CTA
+  if (threads != 512 && threads != 640 && threads != 768 && threads != 1024) return (int)cudaErrorInvalidValue;
+  if (blocks <= 0) blocks = 148;
+  const int per_cta = threads / 16;
+  const long long need = (a.nchunks + per_cta - 1) / per_cta;
+  if (need < blocks) blocks = (int)need;
+  a.flush_scale = flush_scale > 0.f ? flush_scale : 1.f / (float)blocks;
+  const size_t smem = (size_t)hot_T * (2 * 128 + 2) * sizeof(float);
+  if (smem > 220 * 1024) return (int)cudaErrorInvalidValue;
+  cudaError_t e = cudaSuccess;
+#define PCL_H16_LAUNCH(T)                                                                              \
+  e = cudaFuncSetAttribute(mf_sgd_kernel_h16<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+  if (e == cudaSuccess) mf_sgd_kernel_h16<T><<<blocks, T, smem, stream>>>(a);
+  switch (threads) {
+    case 512: PCL_H16_LAUNCH(512) break;
+    case 640: PCL_H16_LAUNCH(640) break;
+    case 768: PCL_H16_LAUNCH(768) break;
+    default: PCL_H16_LAUNCH(1024) break;
+  }
+#undef PCL_H16_LAUNCH
+  if (e != cudaSuccess) return (int)e;
+  return pcl_last_error();
+}

@@ -101,13 +101,18 @@ class MfSgdGpu:
         self.ssp = bool(ssp)
         self.seed = seed
         self.hot_mix = float(hot_mix)
-        # default: 32-lanes-per-rating kernel, 2 CTAs per SM with 16 chunks in flight each;
+        # variant 0: automatic (rank 128 -> sixteen-lanes-per-rating kernel, else the 32-lane one);
+        # variant 1: 32-lanes-per-rating kernel, 2 CTAs per SM with 16 chunks in flight each;
         # variant 2 (D = 128): experimental 8-lanes-per-rating kernel, 1 CTA per SM, 64 chunks
         self.variant = int(variant)
         self.compact = bool(compact)
         self.g8 = (self.D == 128 and self.variant == 2)
-        self.sgd_blocks = int(sgd_blocks) if sgd_blocks > 0 else (148 if self.g8 else 148 * 2)
-        self.warps_per_block = 64 if self.g8 else 16   # chunks in flight per CTA
+        # variant 3 (D = 128): sixteen lanes per rating, two chunks per warp, 1 CTA of 640 threads per SM
+        self.h16 = (self.D == 128 and self.variant in (0, 3))
+        one_cta = self.g8 or self.h16
+        self.sgd_blocks = int(sgd_blocks) if sgd_blocks > 0 else (148 if one_cta else 148 * 2)
+        self.h16_threads = int(os.environ.get("PCL_MF_H16_THREADS", "640"))
+        self.warps_per_block = 64 if self.g8 else (self.h16_threads // 16 if self.h16 else 16)   # chunks in flight per CTA
         self.hot_rows = int(hot_rows)
         self.chunks_per_flush = int(chunks_per_flush)
         self.npx, self.npy = npfact2d(self.world)
@@ -158,7 +163,12 @@ class MfSgdGpu:
         # take the first local indices and are replicated in shared memory
         conc = P * ci.to(torch.float64) / max(nnz, 1)
         T = int(min(self.hot_rows, int((conc > 1.0).sum().item()), self.li.numel()))
-        T = min(T, (220 * 1024) // ((2 * 132 + 2) * 4) if self.g8 else (110 * 1024) // ((2 * self.D + 2) * 4))
+        if self.g8:
+            T = min(T, (220 * 1024) // ((2 * 132 + 2) * 4))
+        elif self.h16:
+            T = min(T, (220 * 1024) // ((2 * 128 + 2) * 4))
+        else:
+            T = min(T, (110 * 1024) // ((2 * self.D + 2) * 4))
         self.hot_T = T
         if T > 0:
             hot = torch.topk(ci, T).indices
@@ -319,7 +329,14 @@ class MfSgdGpu:
 
     def sgd_pass(self):
         s = _lib.stream_ptr()
-        if self.h_ru is None:
+        if self.h_ru is None and self.h16:
+            pk = self.packed if self.compact else None
+            _lib.call("pcl_mf_sgd_pass_h16", self.ru, self.ri, self.rr, self.ru.numel(), self.Wl, self.Hl,
+                      self.bul, self.bil, self.su, self.si, self.mu, self.alpha, self.beta, self.hot_T,
+                      self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, pk,
+                      self.chdr if pk is not None else None, self.rtable if pk is not None else None,
+                      self.h16_threads, s)
+        elif self.h_ru is None:
             pk = self.packed if (self.compact and not self.g8) else None
             _lib.call("pcl_mf_sgd_pass", self.ru, self.ri, self.rr, self.ru.numel(), self.Wl,
                       self.Hl, self.bul, self.bil, self.su, self.si, self.D, self.mu,
@@ -372,15 +389,19 @@ class MfSgdGpu:
                 self._copied[b].record(self.host_stream)
             main.wait_event(self._copied[b])
             if compact:
-                _lib.call("pcl_mf_sgd_pass", None, None, None, m, self.Wl, self.Hl, self.bul, self.bil,
-                          self.su, self.si, self.D, self.mu, self.alpha, self.beta, self.hot_T,
-                          self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, self.variant, bpk, bhd,
-                          self.rtable, main.cuda_stream)
+                seg_args = (None, None, None, bpk, bhd, self.rtable)
             else:
-                _lib.call("pcl_mf_sgd_pass", bru, bri, brr, m, self.Wl, self.Hl, self.bul, self.bil,
-                          self.su, self.si, self.D, self.mu, self.alpha, self.beta, self.hot_T,
-                          self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, self.variant, None, None,
-                          None, main.cuda_stream)
+                seg_args = (bru, bri, brr, None, None, None)
+            if self.h16:
+                _lib.call("pcl_mf_sgd_pass_h16", seg_args[0], seg_args[1], seg_args[2], m, self.Wl, self.Hl,
+                          self.bul, self.bil, self.su, self.si, self.mu, self.alpha, self.beta, self.hot_T,
+                          self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, seg_args[3], seg_args[4],
+                          seg_args[5], self.h16_threads, main.cuda_stream)
+            else:
+                _lib.call("pcl_mf_sgd_pass", seg_args[0], seg_args[1], seg_args[2], m, self.Wl, self.Hl,
+                          self.bul, self.bil, self.su, self.si, self.D, self.mu, self.alpha, self.beta,
+                          self.hot_T, self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, self.variant,
+                          seg_args[3], seg_args[4], seg_args[5], main.cuda_stream)
             self._consumed[b].record(main)
             k += 1
 

@@ -43,6 +43,7 @@ SIGS = {
     "pcl_rows_pull_i32": "ppiiqppp",
     "pcl_rows_push_i32": "ppiiqppip",
     "pcl_mf_sgd_pass": "pppqppppppifffiifipipppp",
+    "pcl_mf_sgd_pass_h16": "pppqppppppfffiifippppip",
     "pcl_mf_sse": "pppqppppifppp",
     "pcl_gemm_tf32": "pppiiiqipppppiiiiipip",
     "pcl_gemm_tf32_2sm": "pppiiiqipppppiiiiipip",

@@ -121,9 +121,10 @@ def test_mf_single_chunk_matches_sequential_oracle():
     from paracel_b200.models.mf_gpu import MfSgdGpu
     dev = "cuda:0"
     g = torch.Generator().manual_seed(3)
-    for k, hot, variant, compact in ((32, 64, 0, True), (80, 64, 0, False), (128, 64, 0, True),
-                                     (128, 0, 0, False), (64, 3, 0, True), (128, 64, 2, True),
-                                     (100, 0, 2, True), (128, 4, 2, True)):
+    for k, hot, variant, compact in ((32, 64, 0, True), (80, 64, 0, False), (128, 64, 1, True),
+                                     (128, 0, 1, False), (64, 3, 0, True), (128, 64, 2, True),
+                                     (100, 0, 2, True), (128, 4, 2, True), (128, 64, 3, True),
+                                     (128, 0, 3, False), (100, 4, 3, True), (128, 5, 3, False)):
         nu, ni, nnz = 6, 9, 31
         u = torch.randint(0, nu, (nnz,), generator=g)
         i = torch.randint(0, ni, (nnz,), generator=g)
@@ -157,9 +158,10 @@ def test_mf_converges_like_sequential_pass():
     dev = "cuda:0"
     _converges(32)
     _converges(128)
+    _converges(128, variant=1)
 
 
-def _converges(k):
+def _converges(k, variant=0):
     from paracel_b200.models.mf_gpu import MfSgdGpu
     from paracel_b200.utils.synth import MfRatingStream
     dev = "cuda:0"
@@ -168,7 +170,7 @@ def _converges(k):
     u, i, r = st.chunk_at(0)
     rounds = 4
     m = MfSgdGpu(nu, ni, k=k, alpha=0.005, beta=0.02, rounds=rounds, device=dev, staleness=0,
-                 ssp=False)
+                 ssp=False, variant=variant)
     m.load_ratings(u, i, r)
     m.init_parameters()
     m.pull()
