@@ -91,7 +91,7 @@ class PageRankGpu:
 
     def step(self, track_delta: bool = False):
         cur, nxt = self.tables[self.it % 2], self.tables[(self.it + 1) % 2]
-        contrib = cur.read()
+        contrib = cur.read(copy=False)   # the pull kernel writes the OTHER table
         if track_delta:
             self.delta_l1.zero_()
         if self.edge_balanced:

@@ -60,6 +60,7 @@ SIGS = {
     "pcl_als_solve": "pppppppppppqifip",
     "pcl_kmeans_accumulate": "ppqippp",
     "pcl_topk_rows": "pqiippfippp",
+    "pcl_balltree_search": "pppppppiiipppp",
     "pcl_partition_count": "ppqiipp",
     "pcl_partition_scatter": "pppqiipqppppip",
     "pcl_gram": "pqipp",

@@ -166,7 +166,11 @@ class DenseTable:
         b = (self.epoch + 1) & 1
         return self.delta_buf.local[b * self.Lp: b * self.Lp + self.L]
 
-    def read(self) -> torch.Tensor:
+    def read(self, copy: bool = True) -> torch.Tensor:
+        """The whole vector.  ``copy=False`` lets a single-rank table return a view of its
+        shard (no kernel); callers that use it must not update the table while they hold it."""
+        if not copy and self.world == 1:
+            return self.shard[: self.L]
         _lib.call("pcl_dense_read", self.theta_buf.ptr_table, self.full, self.Lp, self.S, self.world,
                   self.rank, self.done, self.epoch, self.timeout_ns, self.status, _lib.stream_ptr())
         return self.full[: self.L]

@@ -73,6 +73,47 @@ def linear_search(q: PyQuery, buf) -> List[int]:
     return [i for i, _ in linear_search_with_dp(q, buf)]
 
 
+class DeviceBalltree:
+    """A built ball tree copied to the GPU for batched search (csrc/cuda/balltree.cu)."""
+
+    def __init__(self, tree: PyBalltree, device=None):
+        import torch
+        dev = torch.device(device if device is not None else "cuda")
+        mu, rad, child, rng, order = tree._t.export_arrays()
+        self.dim = tree.items.shape[1]
+        self.n = tree.items.shape[0]
+        self.child = torch.as_tensor(np.asarray(child, dtype=np.int32), device=dev)
+        self.range = torch.as_tensor(np.asarray(rng, dtype=np.int64), device=dev)
+        self.radius = torch.as_tensor(np.asarray(rad, dtype=np.float32), device=dev)
+        self.mu = torch.as_tensor(np.asarray(mu, dtype=np.float32).reshape(-1, self.dim), device=dev)
+        order = np.asarray(order, dtype=np.int64)
+        self.ids = torch.as_tensor(order, device=dev)
+        self.items = torch.as_tensor(tree.items[order].astype(np.float32), device=dev).contiguous()
+        self.device = dev
+
+    def search(self, queries, k: int = 1):
+        """(indices [nq, k], scores [nq, k], balls opened [nq]) for a batch of queries; queries
+        whose traversal overflowed the device stack are answered by a dense product instead."""
+        import torch
+        from ..ops import _lib
+        if not 1 <= k <= 32:
+            raise ValueError("device search supports 1 <= k <= 32")
+        Q = torch.as_tensor(np.asarray(queries, dtype=np.float32), device=self.device).contiguous()
+        nq = Q.shape[0]
+        idx = torch.empty(nq, k, dtype=torch.int64, device=self.device)
+        sc = torch.empty(nq, k, dtype=torch.float32, device=self.device)
+        vis = torch.empty(nq, dtype=torch.int32, device=self.device)
+        _lib.call("pcl_balltree_search", self.child, self.range, self.radius, self.mu, self.items, self.ids,
+                  Q, self.dim, nq, k, idx, sc, vis, _lib.stream_ptr())
+        bad = torch.nonzero(vis < 0).flatten()
+        if bad.numel():
+            S = Q[bad] @ self.items.T
+            s2, j2 = torch.topk(S, min(k, self.n), dim=1)
+            idx[bad, : j2.shape[1]] = self.ids[j2]
+            sc[bad, : j2.shape[1]] = s2
+        return idx, sc, vis
+
+
 def search_batch_gpu(queries, items, k: int):
     """Top-k inner products for a batch of queries on the GPU: (indices, scores)."""
     import torch

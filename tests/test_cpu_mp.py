@@ -221,3 +221,23 @@ def test_lda_two_workers_likelihood_improves(tmp_path):
     assert ll[-1] > ll[0] + 500
     lines = open(out + "0").read().strip().split("\n") + open(out + "1").read().strip().split("\n")
     assert len([l for l in lines if l]) == 3 and all("topic\t" in l and l.endswith("|") for l in lines if l)
+
+
+def test_bsp_runs_are_deterministic(tmp_path):
+    """Same input, same seed, BSP mode: two jobs write byte-identical model dumps."""
+    rng = np.random.default_rng(2)
+    X = np.concatenate([rng.normal(0, 0.3, (40, 3)), rng.normal(4, 0.3, (40, 3))])
+    p = tmp_path / "km.txt"
+    p.write_text("".join("%d\t%s\n" % (i, ",".join("%.6f" % v for v in X[i])) for i in range(80)))
+    edges = [(1, 2), (1, 3), (2, 3), (3, 1), (4, 3), (4, 1), (5, 4), (2, 5)]
+    g = tmp_path / "pr.txt"
+    g.write_text("".join(f"{a},{b}\n" for a, b in edges))
+    dumps = []
+    for trial in range(2):
+        out_k, out_p = str(tmp_path / f"km{trial}"), str(tmp_path / f"pr{trial}")
+        LocalJob(2, 1).run(W.run_kmeans, (str(p), out_k, 2, 5), timeout_s=300)
+        LocalJob(2, 2).run(W.run_pagerank, (str(g), out_p, 8), timeout_s=300)
+        dumps.append((open(os.path.join(out_k, "centers_0"), "rb").read(),
+                      open(os.path.join(out_k, "kmeans_0"), "rb").read(),
+                      open(os.path.join(out_p, "pagerank_0"), "rb").read()))
+    assert dumps[0] == dumps[1]

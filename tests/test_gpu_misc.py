@@ -94,3 +94,32 @@ def test_device_allreduce_single_rank():
     ar.check()
     assert torch.equal(x, y)
     ar.free()
+
+
+def test_device_balltree_search_matches_host_tree_and_brute_force():
+    import numpy as np
+    from paracel_b200.tool.balltree import DeviceBalltree, PyBalltree, PyQuery, balltree_search_with_dp
+    rng = np.random.default_rng(4)
+    items = rng.standard_normal((6000, 24)) * rng.uniform(0.2, 2.0, (6000, 1))
+    tree = PyBalltree(items)
+    tree.build()
+    dt = DeviceBalltree(tree)
+    queries = rng.standard_normal((300, 24))
+    k = 7
+    idx, sc, vis = dt.search(queries, k)
+    torch.cuda.synchronize()
+    idx, sc, vis = idx.cpu().numpy(), sc.cpu().numpy(), vis.cpu().numpy()
+    exact = (queries @ items.T)
+    ref_idx = np.argsort(-exact, axis=1)[:, :k]
+    ref_sc = np.take_along_axis(exact, ref_idx, axis=1)
+    assert np.allclose(sc, ref_sc, rtol=1e-4, atol=1e-4)          # same scores as brute force
+    assert (idx == ref_idx).mean() > 0.995                          # ids differ only on fp32 near-ties
+    assert np.all(np.diff(sc, axis=1) <= 1e-6)                      # best first
+    assert vis.min() > 0 and vis.mean() < 0.6 * tree.node_count     # pruning happened
+    host = balltree_search_with_dp(PyQuery(list(queries[0]), k), tree)
+    assert [i for i, _ in host] == list(idx[0])
+    # fewer items than k
+    small = PyBalltree(items[:3])
+    small.build()
+    i2, s2, _ = DeviceBalltree(small).search(queries[:2], 5)
+    assert (i2[:, 3:] == -1).all().item() and sorted(i2[0, :3].tolist()) == [0, 1, 2]
