@@ -47,6 +47,9 @@ def parse_args():
     ap.add_argument("--staleness", type=int, default=2)
     ap.add_argument("--seed", type=int, default=20240611)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--spread-above", type=float, default=0.25,
+                    help="ids holding more than this fraction of one group's share are dealt over all "
+                         "ranks of the grid row / column (0: never)")
     ap.add_argument("--phases", action="store_true",
                     help="after the timed steps run two extra rounds with per-phase device timing")
     ap.add_argument("--no-balance", action="store_true")
@@ -95,7 +98,7 @@ def main():
         from paracel_b200.baselines.mf_nccl_torch import MfSgdNcclTorch as Model
     else:
         from paracel_b200.models.mf_gpu import MfSgdGpu as Model
-    from paracel_b200.models.mf_gpu import balanced_groups
+    from paracel_b200.models.mf_gpu import balanced_groups, grid_rank
 
     K, Wm = args.steps, args.warmup
     total_rounds = 2 * (K + Wm) + 4
@@ -111,8 +114,8 @@ def main():
                             device=dev)
     if world > 1 and not args.no_balance:
         cu, ci = stream.counts()
-        ugrp = balanced_groups(cu, model.npx)
-        igrp = balanced_groups(ci, model.npy)
+        ugrp = balanced_groups(cu, model.npx, spread_above=args.spread_above)
+        igrp = balanced_groups(ci, model.npy, spread_above=args.spread_above)
     else:
         ar_u = torch.arange(args.users, device=dev)
         ar_i = torch.arange(args.items, device=dev)
@@ -121,7 +124,7 @@ def main():
     us, is_, rs = [], [], []
     for u, i, r in stream:
         if world > 1:
-            keep = (ugrp[u].to(torch.int64) * model.npy + igrp[i].to(torch.int64)) == rank
+            keep = grid_rank(u, i, ugrp, igrp, model.npx, model.npy) == rank
             u, i, r = u[keep], i[keep], r[keep]
         us.append(u.to(torch.int32))
         is_.append(i.to(torch.int32))
@@ -180,6 +183,11 @@ def main():
             model.round()
         phases = model.phase_times_ms()
         model.phase_timing = False
+        if world > 1:
+            allp = [None] * world
+            dist.all_gather_object(allp, phases)
+            phases = {"rank0": phases,
+                      "sgd_ms_per_rank": [round(p.get("sgd", 0.0), 3) for p in allp]}
         barrier()
 
     # ---- end to end: ratings streamed from pinned host memory each round

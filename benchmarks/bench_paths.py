@@ -30,6 +30,9 @@ def main():
     ap.add_argument("--path", required=True, choices=["rows", "dense", "gather_gemm", "ssp", "allreduce"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--small", action="store_true", help="smaller sizes (for ncu captures)")
+    ap.add_argument("--table-rows", type=int, default=0, help="rows path: total table rows (default 4 M per rank)")
+    ap.add_argument("--push-rows", type=int, default=0, help="rows path: rows pulled / pushed per rank")
+    ap.add_argument("--sorted-ids", action="store_true", help="rows path: ascending ids instead of a random order")
     ap.add_argument("--kernel", default=None, choices=["1sm", "2sm"], help="GEMM kernel of gather_gemm")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -76,11 +79,14 @@ def main():
     if args.path == "rows":
         from paracel_b200.ps.tables import RowTable
         rows = (1 << 20) if args.small else (1 << 22)
-        t = RowTable(rows * world, 128, torch.float32)
+        total_rows = args.table_rows or rows * world
+        t = RowTable(total_rows, 128, torch.float32)
         t.shard.normal_()
-        n = rows // 2
+        n = args.push_rows or rows // 2
         g = torch.Generator(device=dev).manual_seed(1 + rank)
-        ids = torch.randperm(rows * world, device=dev, generator=g)[:n].contiguous()
+        ids = torch.randperm(total_rows, device=dev, generator=g)[:n].contiguous()
+        if args.sorted_ids:
+            ids = torch.sort(ids).values.contiguous()
         cur = torch.empty(n, 128, device=dev)
         old = torch.empty_like(cur)
         wgt = torch.rand(n, device=dev)
@@ -88,6 +94,7 @@ def main():
         ms_pull = timeit(lambda: t.pull(ids, cur, old))
         cur += 1.0
         ms_push = timeit(lambda: t.push(ids, cur, old, wgt, refresh_old=False))
+
         row_b = 512.0
         remote = (world - 1) / world
         out.update({

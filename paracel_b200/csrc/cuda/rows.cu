@@ -76,6 +76,7 @@ struct PushArgs {
   float scale;         // extra scale for H_SCALED_ADD
   int handler;
   int refresh_old;     // write old = cur after pushing
+  long long start;     // rows are visited in the order start, start+1, .., n-1, 0, .., start-1
 };
 
 __device__ __forceinline__ void atomic_max_f32(float* p, float v) {
@@ -91,8 +92,13 @@ __global__ void __launch_bounds__(256) rows_push_kernel(PushArgs a) {
   const int rows_per_block = blockDim.x / tpr;
   const int sub = threadIdx.x % tpr;
   const int rib = threadIdx.x / tpr;
-  for (long long row = (long long)blockIdx.x * rows_per_block + rib; row < a.n;
-       row += (long long)gridDim.x * rows_per_block) {
+  for (long long it = (long long)blockIdx.x * rows_per_block + rib; it < a.n;
+       it += (long long)gridDim.x * rows_per_block) {
+    // ranks that hold the same rows (same grid row / column of the loader's partition) pass
+    // different `start` values, so that they do not reduce into the same destination rows at
+    // the same moment
+    long long row = it + a.start;
+    if (row >= a.n) row -= a.n;
     long long g = a.ids[row];
     int owner = (int)(g % a.world);
     long long lrow = g / a.world;
@@ -233,11 +239,12 @@ PCL_API int pcl_rows_pull_f32(const long long* ids, float* const* shards, int wo
 
 PCL_API int pcl_rows_push_f32(const long long* ids, float* const* shards, int world, int D,
                               long long n, float* cur, float* old, const float* wgt,
-                              float scale, int handler, int refresh_old,
+                              float scale, int handler, int refresh_old, long long start,
                               cudaStream_t stream) {
   if (D <= 0 || (D & 3)) return (int)cudaErrorInvalidValue;
   if (n <= 0) return 0;
-  PushArgs a{ids, shards, world, D, n, cur, old, wgt, scale, handler, refresh_old};
+  if (start < 0 || start >= n) start = 0;
+  PushArgs a{ids, shards, world, D, n, cur, old, wgt, scale, handler, refresh_old, start};
   int vec = D >> 2, tpr = 32;
   while (tpr > vec) tpr >>= 1;
   int grid = grid_for(n, 256 / tpr, 148 * 16);

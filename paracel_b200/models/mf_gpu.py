@@ -21,7 +21,7 @@ from __future__ import annotations
 
 import math
 import os
-from typing import Optional
+from typing import Dict, Optional
 
 import torch
 import torch.distributed as dist
@@ -39,7 +39,7 @@ def _pad_rank(k: int) -> int:
     raise ValueError("factor rank above 256 is not supported by the SGD kernel")
 
 
-def balanced_groups(counts: torch.Tensor, ngroups: int) -> torch.Tensor:
+def balanced_groups(counts: torch.Tensor, ngroups: int, spread_above: float = 0.0) -> torch.Tensor:
     """Assign ids to ``ngroups`` groups with near-equal total count.
 
     The ``heavy`` ids (count above 1/(64*ngroups) of the total) are placed greedily, largest
@@ -47,6 +47,12 @@ def balanced_groups(counts: torch.Tensor, ngroups: int) -> torch.Tensor:
     target: a tail id goes to group g with a share proportional to the group's remaining
     deficit, spread evenly over the popularity ranks by a golden-ratio sequence (so a group
     that already holds a very popular id receives few tail ids instead of an equal part).
+
+    ``spread_above`` > 0 marks ids whose count exceeds ``spread_above / ngroups`` of the total
+    with group -1: their entries are meant to be dealt over ALL groups by the other coordinate
+    (see :func:`grid_rank`), which keeps one extremely popular row from making one group of
+    ranks spend most of its pass on a single row; their mass counts as evenly divided here.
+
     Returns an int32 group id per id.  With ``ngroups == 1`` everything is group 0.
     """
     n = counts.numel()
@@ -55,21 +61,26 @@ def balanced_groups(counts: torch.Tensor, ngroups: int) -> torch.Tensor:
     if ngroups == 1:
         return grp
     total = float(counts.sum().item())
+    c64 = counts.to(torch.float64)
+    spread = torch.zeros(n, dtype=torch.bool, device=dev)
+    if spread_above > 0.0:
+        spread = c64 > (spread_above / ngroups) * total
+    spread_mass = float(c64[spread].sum().item())
     thresh = total / (64.0 * ngroups)
-    heavy = torch.nonzero(counts.to(torch.float64) > thresh).flatten()
-    if heavy.numel() == 0:
-        return grp
-    hc = counts[heavy].to(torch.float64)
-    order = torch.argsort(hc, descending=True)
-    heavy, hc = heavy[order].cpu(), hc[order].cpu()
-    load = torch.zeros(ngroups, dtype=torch.float64)
+    heavy = torch.nonzero((c64 > thresh) & ~spread).flatten()
+    load = torch.full((ngroups,), spread_mass / ngroups, dtype=torch.float64)
     g_heavy = torch.empty(heavy.numel(), dtype=torch.int32)
-    for j in range(heavy.numel()):
-        g = int(torch.argmin(load))
-        g_heavy[j] = g
-        load[g] += hc[j]
-    light_mask = torch.ones(n, dtype=torch.bool, device=dev)
-    light_mask[heavy.to(dev)] = False
+    if heavy.numel():
+        hc = c64[heavy]
+        order = torch.argsort(hc, descending=True)
+        heavy, hc = heavy[order].cpu(), hc[order].cpu()
+        for j in range(heavy.numel()):
+            g = int(torch.argmin(load))
+            g_heavy[j] = g
+            load[g] += hc[j]
+    light_mask = ~spread
+    if heavy.numel():
+        light_mask[heavy.to(dev)] = False
     light = torch.nonzero(light_mask).flatten()
     deficit = torch.clamp(total / ngroups - load, min=0.0)
     if float(deficit.sum()) <= 0.0:
@@ -78,8 +89,24 @@ def balanced_groups(counts: torch.Tensor, ngroups: int) -> torch.Tensor:
     edges[-1] = 1.0
     x = torch.frac(torch.arange(light.numel(), device=dev, dtype=torch.float64) * 0.6180339887498949)
     grp[light] = torch.clamp(torch.searchsorted(edges, x, right=True), max=ngroups - 1).to(torch.int32)
-    grp[heavy.to(dev)] = g_heavy.to(dev)
+    if heavy.numel():
+        grp[heavy.to(dev)] = g_heavy.to(dev)
+    grp[spread] = -1
     return grp
+
+
+def grid_rank(u: torch.Tensor, i: torch.Tensor, ugrp: torch.Tensor, igrp: torch.Tensor,
+              npx: int, npy: int) -> torch.Tensor:
+    """Rank (grid row * npy + grid column) of every rating under the group tables of
+    :func:`balanced_groups`.  The ratings of a user (item) marked -1 are dealt round-robin over
+    the grid rows (columns) by their position in the list, so that row is shared by every rank
+    of the grid row (column) whatever the popularity of the other coordinate."""
+    gu = ugrp[u].to(torch.int64)
+    gi = igrp[i].to(torch.int64)
+    pos = torch.arange(u.numel(), device=u.device, dtype=torch.int64)
+    gu = torch.where(gu < 0, pos % npx, gu)
+    gi = torch.where(gi < 0, pos % npy, gi)
+    return gu * npy + gi
 
 
 class MfSgdGpu:
@@ -129,6 +156,10 @@ class MfSgdGpu:
         self.host_stream = None
         self.h2d_bytes = 0
         self._loaded = False
+        # push + commit of round t on a side stream, overlapped with the SGD pass of round t+1
+        self.overlap_push = os.environ.get("PCL_MF_OVERLAP_PUSH", "1") != "0"
+        self._push_stream = None
+        self._push_done = None
         # optional per-phase device timing of round() (diagnostics; adds event records only)
         self.phase_timing = False
         self._phase_events = []
@@ -208,6 +239,11 @@ class MfSgdGpu:
         conc_i[: self.hot_T] = float(min(self.warps_per_block, P))  # replicas: per-CTA concurrency
         self.si = (1.0 / torch.clamp(self.hot_mix * conc_i * ci.to(torch.float32) / denom, min=1.0)).contiguous()
         nU, nI = self.lu.numel(), self.li.numel()
+        # user rows are shared by the ranks of this grid row, item rows by those of this grid
+        # column: every sharer starts its push at a different place of the (sorted) id list
+        stagger = os.environ.get("PCL_MF_STAGGER", "1") != "0"
+        self._start_u = (self.py * nU) // max(self.npy, 1) if stagger else 0
+        self._start_i = (self.px * nI) // max(self.npx, 1) if stagger else 0
         self.Wl = torch.empty(nU, self.D, device=dev)
         self.W0 = torch.empty(nU, self.D, device=dev)
         self.Hl = torch.empty(nI, self.D, device=dev)
@@ -421,43 +457,111 @@ class MfSgdGpu:
             return True
         return (c - self._pulled_at) >= self.staleness
 
-    def _mark(self):
+    def _mark(self, label: str):
         if self.phase_timing:
             e = torch.cuda.Event(enable_timing=True)
             e.record()
-            self._phase_events.append(e)
+            self._phase_events.append((label, e))
+
+    def _push_sync(self):
+        probe = os.environ.get("PCL_MF_PUSH_PROBE", "")
+        if probe == "sync":
+            self._barrier()
+            self._mark("probe_barrier")
+        if probe == "norefresh":
+            self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u, start=self._start_u, refresh_old=False)
+        elif probe == "clone":
+            tmp = self.Wl.clone()
+            self._mark("probe_clone")
+            self.Wt.push(self.lu, tmp, self.W0, self.wgt_u, start=self._start_u)
+        elif probe == "twice":
+            self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u, start=self._start_u)
+            self._mark("push_W_first")
+            self.Wl += 1e-3
+            self._mark("probe_add")
+            self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u, start=self._start_u)
+        else:
+            self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u, start=self._start_u)
+        self._mark("push_W")
+        self.Ht.push(self.li, self.Hl, self.H0, self.wgt_i, start=self._start_i)
+        self._mark("push_H")
+        self.but.push(self.lu, self.bul, self.bu0, self.wgt_u)
+        self.bit.push(self.li, self.bil, self.bi0, self.wgt_i)
+        self._mark("push_bias")
+        if not self.ssp and self.world > 1:
+            self._barrier()
+        self.clock.commit()
+        self._mark("commit")
+
+    def _push_overlapped(self):
+        """Push + commit on a side stream while the main stream goes on with the next round.
+
+        The working copies are first copied to staging buffers (local, one pass); the side
+        stream then reduces ``wgt * (staged - snapshot)`` into the owners' shards, refreshes
+        the snapshots and commits the clock.  The peers' reductions arrive while every GPU is
+        busy with its next SGD pass instead of holding the round up.  Used with a staleness
+        bound of at least 2: this rank's own clock may then lag one commit behind without
+        ever blocking its own wait."""
+        dev = self.device
+        main = torch.cuda.current_stream(dev)
+        if self._push_stream is None:
+            self._push_stream = torch.cuda.Stream(device=dev)
+            self._Ws = torch.empty_like(self.Wl)
+            self._Hs = torch.empty_like(self.Hl)
+            self._bus = torch.empty_like(self.bul)
+            self._bis = torch.empty_like(self.bil)
+        if self._push_done is not None:
+            main.wait_event(self._push_done)      # staging buffers are free again
+        self._Ws.copy_(self.Wl)
+        self._Hs.copy_(self.Hl)
+        self._bus.copy_(self.bul)
+        self._bis.copy_(self.bil)
+        staged = torch.cuda.Event()
+        staged.record(main)
+        self._mark("stage")
+        with torch.cuda.stream(self._push_stream):
+            self._push_stream.wait_event(staged)
+            self.Wt.push(self.lu, self._Ws, self.W0, self.wgt_u, start=self._start_u)
+            self.Ht.push(self.li, self._Hs, self.H0, self.wgt_i, start=self._start_i)
+            self.but.push(self.lu, self._bus, self.bu0, self.wgt_u)
+            self.bit.push(self.li, self._bis, self.bi0, self.wgt_i)
+            self.clock.commit()
+            self._push_done = torch.cuda.Event()
+            self._push_done.record(self._push_stream)
 
     def round(self):
-        self._mark()
+        self._mark("start")
         if self.need_pull():
+            if self._push_done is not None:       # the pull must see this rank's own pushes
+                torch.cuda.current_stream(self.device).wait_event(self._push_done)
             self.pull()
             self._pulled_at = self.clock.clock
         elif self.world > 1:
             self.clock.wait()  # keep the staleness bound while serving from the cache
-        self._mark()
+        self._mark("pull_or_wait")
         self.sse.zero_()
         self.sgd_pass()
-        self._mark()
-        self.push()
-        if not self.ssp and self.world > 1:
-            self._barrier()
-        self.clock.commit()
-        self._mark()
+        self._mark("sgd")
+        if self.overlap_push and self.world > 1 and self.ssp and self.staleness >= 2:
+            self._push_overlapped()
+        else:
+            self._push_sync()
 
     def phase_times_ms(self):
-        """Mean device time of the pull-or-wait / SGD / push+commit phases over the rounds run
-        since ``phase_timing`` was switched on (synchronises)."""
+        """Mean device time of each phase of round() over the rounds run since ``phase_timing``
+        was switched on (synchronises)."""
         torch.cuda.synchronize(self.device)
-        ev = self._phase_events
-        n = len(ev) // 4
-        out = {"pull_or_wait": 0.0, "sgd": 0.0, "push_commit": 0.0, "rounds": n}
-        for r in range(n):
-            a, b, c, d = ev[4 * r: 4 * r + 4]
-            out["pull_or_wait"] += a.elapsed_time(b)
-            out["sgd"] += b.elapsed_time(c)
-            out["push_commit"] += c.elapsed_time(d)
-        for k in ("pull_or_wait", "sgd", "push_commit"):
-            out[k] = out[k] / max(n, 1)
+        out: Dict[str, float] = {}
+        rounds = 0
+        prev = None
+        for label, e in self._phase_events:
+            if label == "start":
+                rounds += 1
+            else:
+                out[label] = out.get(label, 0.0) + prev.elapsed_time(e)
+            prev = e
+        out = {k: v / max(rounds, 1) for k, v in out.items()}
+        out["rounds"] = rounds
         self._phase_events = []
         return out
 

@@ -37,7 +37,7 @@ SIGS = {
     "pcl_symm_free": "p",
     "pcl_device_sync": "",
     "pcl_rows_pull_f32": "ppiiqpppqQpip",
-    "pcl_rows_push_f32": "ppiiqpppfiip",
+    "pcl_rows_push_f32": "ppiiqpppfiiqp",
     "pcl_scalars_pull_f32": "ppiqppp",
     "pcl_scalars_push_f32": "ppiqpppip",
     "pcl_rows_pull_i32": "ppiiqppp",

@@ -62,14 +62,16 @@ class RowTable:
 
     def push(self, ids: torch.Tensor, cur: torch.Tensor, old: Optional[torch.Tensor] = None,
              wgt: Optional[torch.Tensor] = None, handler: str = "add", scale: float = 1.0,
-             refresh_old: bool = True):
+             refresh_old: bool = True, start: int = 0):
+        """``start``: first row of ``ids`` to visit (the kernel wraps around).  Ranks that push the
+        same rows at the same time should pass different values."""
         _lib.check_cuda(ids, torch.int64, "ids")
         _lib.check_cuda(cur, self.dtype, "cur")
         n = ids.numel()
         s = _lib.stream_ptr()
         if self.dtype == torch.float32:
             _lib.call("pcl_rows_push_f32", ids, self.buf.ptr_table, self.world, self.width, n,
-                      cur, old, wgt, float(scale), HANDLERS[handler], int(refresh_old), s)
+                      cur, old, wgt, float(scale), HANDLERS[handler], int(refresh_old), int(start), s)
         else:
             if handler != "add" or wgt is not None:
                 raise ValueError("int32 tables support the add handler only")

@@ -109,7 +109,7 @@ def ssp_clock(comm, server_info):
 
 
 def mf_train(comm, server_info, nu, ni, nnz, k, rounds, staleness):
-    from paracel_b200.models.mf_gpu import MfSgdGpu, balanced_groups
+    from paracel_b200.models.mf_gpu import MfSgdGpu, balanced_groups, grid_rank
     from paracel_b200.utils.synth import MfRatingStream
     rank, world = comm.get_rank(), comm.get_size()
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -119,8 +119,8 @@ def mf_train(comm, server_info, nu, ni, nnz, k, rounds, staleness):
                  ssp=staleness > 0, seed=3)
     cu = torch.bincount(u, minlength=nu)
     ci = torch.bincount(i, minlength=ni)
-    ug, ig = balanced_groups(cu, m.npx), balanced_groups(ci, m.npy)
-    keep = (ug[u].to(torch.int64) * m.npy + ig[i].to(torch.int64)) == rank
+    ug, ig = balanced_groups(cu, m.npx, spread_above=0.25), balanced_groups(ci, m.npy, spread_above=0.25)
+    keep = grid_rank(u, i, ug, ig, m.npx, m.npy) == rank
     m.load_ratings(u[keep], i[keep], r[keep])
     m.init_parameters()
     m.pull()
