@@ -44,14 +44,28 @@ __global__ void __launch_bounds__(256) dense_read_kernel(ReadArgs a) {
   const long long nvec = a.L >> 2;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nth = (long long)gridDim.x * blockDim.x;
-  for (long long v = tid; v < nvec; v += nth) {
-    const long long e = v << 2;
-    // visit the shards in ring order starting from this rank to spread the switch load
-    int owner = (int)(e / a.S);
-    if (owner >= a.world) owner = a.world - 1;
-    const float* src = a.shards[owner] + (e - (long long)owner * a.S);
-    const float4 x = pcl_ld_sys4(src);
-    *reinterpret_cast<float4*>(a.out + e) = x;
+  // Ring order: rank r starts with its own shard and walks r+1, r+2, ...; at any moment the
+  // ranks read from different owners instead of all from shard 0.  Four loads in flight per thread.
+  const long long shift = ((long long)a.rank * a.S) >> 2;   // S is a multiple of 4
+  for (long long v0 = tid; v0 < nvec; v0 += 4 * nth) {
+    float4 x[4];
+    long long e[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long v = v0 + u * nth;
+      e[u] = -1;
+      if (v < nvec) {
+        long long vv = v + shift;
+        if (vv >= nvec) vv -= nvec;
+        e[u] = vv << 2;
+        int owner = (int)(e[u] / a.S);
+        if (owner >= a.world) owner = a.world - 1;
+        x[u] = pcl_ld_sys4(a.shards[owner] + (e[u] - (long long)owner * a.S));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (e[u] >= 0) *reinterpret_cast<float4*>(a.out + e[u]) = x[u];
   }
   for (long long e = (nvec << 2) + tid; e < a.L; e += nth) {
     int owner = (int)(e / a.S);

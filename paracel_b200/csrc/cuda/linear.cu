@@ -202,7 +202,7 @@ PCL_API int pcl_lr_sparse_grad(const long long* row_ptr, const int* cols, const 
 // Allocation-free variant of the dense gradient (declared in pcl_noalloc.h).
 //
 // Some hosts of this library may not call cudaMalloc at all: a serving process
-// that handed its whole HBM budget to one arena at start-up, a plug-in that runs
+// that handed all of its HBM to one arena at start-up, a plug-in that runs
 // inside somebody else's memory pool, or a latency-critical loop where the
 // implicit device synchronisation of cudaMalloc/cudaFree is not acceptable.  For
 // them the block partials and the block counter of dense_grad_kernel live in

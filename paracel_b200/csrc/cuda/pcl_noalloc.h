@@ -3,7 +3,7 @@
 // This has no counterpart in the reference (douban/paracel has no GPU code and
 // no notion of device allocation); it exists for embedders of this library.
 //
-// Who needs it: a process that gave its whole device-memory budget to one arena
+// Who needs it: a process that gave all of its device memory to one arena
 // when it started (an inference or feature server, a database engine), code
 // that runs as a plug-in inside another framework's memory pool, and tight
 // control loops that cannot afford the device-wide synchronisation cudaMalloc

@@ -78,7 +78,7 @@ class KMeansGpu:
     def round(self):
         lo, hi = self.centres.local_rows()
         # |c|^2 of every centre: owners know their rows, the rest comes with the gathered copy of
-        # the previous call; computed from a small all-gather to stay exact in round 0
+        # the previous call; computed from a small all-gather to stay exact in the first round
         shard_norm = (self.c_local * self.c_local).sum(1)
         if self.world > 1:
             parts = [torch.empty_like(shard_norm) for _ in range(self.world)]
