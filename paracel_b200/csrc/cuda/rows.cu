@@ -113,7 +113,6 @@ __global__ void __launch_bounds__(256) rows_push_kernel(PushArgs a) {
       if (o) {
         float4 y = *reinterpret_cast<const float4*>(o + 4 * v);
         d.x -= y.x; d.y -= y.y; d.z -= y.z; d.w -= y.w;
-        if (a.refresh_old) *reinterpret_cast<float4*>(o + 4 * v) = x;
       }
       if (a.handler == H_MAX) {
         atomic_max_f32(dstp + 4 * v + 0, x.x);
@@ -125,6 +124,20 @@ __global__ void __launch_bounds__(256) rows_push_kernel(PushArgs a) {
         if (d.x != 0.f || d.y != 0.f || d.z != 0.f || d.w != 0.f)
           pcl_red_add4_sys(dstp + 4 * v, d);
       }
+    }
+  }
+  // Snapshot refresh (old = cur) as a second sweep over the same elements.  Interleaving these
+  // stores with the system-scope reductions of the first sweep made the kernel about five times
+  // slower on NVLink (1.5 ms instead of 0.2 ms for one million rows of 512 bytes).
+  if (a.old != nullptr && a.refresh_old) {
+    for (long long it = (long long)blockIdx.x * rows_per_block + rib; it < a.n;
+         it += (long long)gridDim.x * rows_per_block) {
+      long long row = it + a.start;
+      if (row >= a.n) row -= a.n;
+      const float* c = a.cur + row * a.D;
+      float* o = a.old + row * a.D;
+      for (int v = sub; v < vec_per_row; v += tpr)
+        *reinterpret_cast<float4*>(o + 4 * v) = *reinterpret_cast<const float4*>(c + 4 * v);
     }
   }
 }
@@ -160,10 +173,14 @@ __global__ void scalars_push_kernel(ScalarArgs a) {
     float* dstp = a.shards[(int)(g % a.world)] + g / a.world;
     float x = a.cur[i];
     float d = a.old ? x - a.old[i] : x;
-    if (a.old && a.refresh_old) a.old[i] = x;
     if (a.wgt) d *= a.wgt[i];
     if (d != 0.f)
       asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(dstp), "f"(d) : "memory");
+  }
+  if (a.old != nullptr && a.refresh_old) {   // second sweep, see rows_push_kernel
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n;
+         i += (long long)gridDim.x * blockDim.x)
+      a.old[i] = a.cur[i];
   }
 }
 
@@ -206,11 +223,15 @@ __global__ void __launch_bounds__(256) irows_push_kernel(IRowArgs a) {
     for (int e = lane; e < a.D; e += 32) {
       int x = a.cur[row * a.D + e];
       int d = a.old ? x - a.old[row * a.D + e] : x;
-      if (a.old && a.refresh_old) a.old[row * a.D + e] = x;
       if (d != 0)
         asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(dstp + e), "r"(d)
                      : "memory");
     }
+  }
+  if (a.old != nullptr && a.refresh_old) {   // second sweep, see rows_push_kernel
+    for (long long row = (long long)blockIdx.x * wpb + warp; row < a.n;
+         row += (long long)gridDim.x * wpb)
+      for (int e = lane; e < a.D; e += 32) a.old[row * a.D + e] = a.cur[row * a.D + e];
   }
 }
 

@@ -156,8 +156,9 @@ class MfSgdGpu:
         self.host_stream = None
         self.h2d_bytes = 0
         self._loaded = False
-        # push + commit of round t on a side stream, overlapped with the SGD pass of round t+1
-        self.overlap_push = os.environ.get("PCL_MF_OVERLAP_PUSH", "1") != "0"
+        # optional (PCL_MF_OVERLAP_PUSH=1): push + commit of round t on a side stream, overlapped with
+        # the SGD pass of round t+1; off by default since the push itself takes well under a millisecond
+        self.overlap_push = os.environ.get("PCL_MF_OVERLAP_PUSH", "0") == "1"
         self._push_stream = None
         self._push_done = None
         # optional per-phase device timing of round() (diagnostics; adds event records only)
@@ -464,24 +465,7 @@ class MfSgdGpu:
             self._phase_events.append((label, e))
 
     def _push_sync(self):
-        probe = os.environ.get("PCL_MF_PUSH_PROBE", "")
-        if probe == "sync":
-            self._barrier()
-            self._mark("probe_barrier")
-        if probe == "norefresh":
-            self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u, start=self._start_u, refresh_old=False)
-        elif probe == "clone":
-            tmp = self.Wl.clone()
-            self._mark("probe_clone")
-            self.Wt.push(self.lu, tmp, self.W0, self.wgt_u, start=self._start_u)
-        elif probe == "twice":
-            self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u, start=self._start_u)
-            self._mark("push_W_first")
-            self.Wl += 1e-3
-            self._mark("probe_add")
-            self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u, start=self._start_u)
-        else:
-            self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u, start=self._start_u)
+        self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u, start=self._start_u)
         self._mark("push_W")
         self.Ht.push(self.li, self.Hl, self.H0, self.wgt_i, start=self._start_i)
         self._mark("push_H")
