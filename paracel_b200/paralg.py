@@ -203,6 +203,32 @@ class paralg:
         self.set_decomp_info(pattern)
         return out
 
+    def paracel_load_as_matrix_device(self, fn, parser: Callable = parser_a, pattern: str = "fsmap",
+                                      mix_flag: bool = False, group=None, device=None):
+        """Sparse load with numeric ids whose placement, exchange, renumbering and CSR build run
+        on the GPUs (``load/device_exchange.py``): every rank parses its share of the lines,
+        copies the (row, col, weight) triples to its device, and the triples travel to their
+        owners by peer stores.  Returns ``(rowptr int64, col int32, val fp32, rm, cm)`` as device
+        tensors; ``rm[i]`` / ``cm[j]`` are the original ids of local row i / column j, exactly the
+        maps ``paracel_load_as_matrix`` returns for the same file and pattern."""
+        import numpy as np
+        import torch
+        from .load.device_exchange import DeviceExchange
+        ld = loader(fn, self.worker_comm, parser, pattern, mix_flag)
+        lines = ld.fixload()
+        self.paracel_sync()
+        from .load.scheduler import scheduler
+        slots = scheduler(self.worker_comm, pattern, mix_flag).lines_organize(lines, parser, numeric=True)
+        trip = [t for slot in slots for t in slot]
+        dev = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        a = torch.as_tensor(np.asarray([t[0] for t in trip], dtype=np.int64), device=dev)
+        b = torch.as_tensor(np.asarray([t[1] for t in trip], dtype=np.int64), device=dev)
+        w = torch.as_tensor(np.asarray([t[2] for t in trip], dtype=np.float32), device=dev)
+        ex = DeviceExchange(pattern, group, dev)
+        out = ex.load(a, b, w)
+        self.set_decomp_info(pattern)
+        return out
+
     # -------------------------------------------------------- registration
     def paracel_register_update(self, file_name: str, func_name: str) -> bool:
         self.update_f = None if not func_name else self._local_handler(file_name, func_name)

@@ -85,3 +85,30 @@ def test_device_exchange_single_rank_csr():
     # columns ascend inside every row
     same_row = rows[1:] == rows[:-1]
     assert bool((col[1:][same_row] >= col[:-1][same_row]).all())
+
+
+def test_paralg_device_matrix_load_matches_host_loader(tmp_path):
+    """Same file through the host loader (scipy CSR) and the device loader: same maps, same matrix."""
+    import numpy as np
+    from paracel_b200.load.parser import gen_parser, parser_a
+    from paracel_b200.paralg import paralg
+    from paracel_b200.parallel.comm import Comm
+    rng = np.random.default_rng(8)
+    rows = rng.integers(0, 200, 3000) * 3 + 1
+    cols = rng.integers(0, 150, 3000) * 2
+    vals = rng.random(3000).round(4)
+    seen = {}
+    for r, c, v in zip(rows, cols, vals):
+        seen[(int(r), int(c))] = float(v)          # unique (row, col) pairs
+    p = tmp_path / "m.txt"
+    p.write_text("".join(f"{r},{c},{v}\n" for (r, c), v in seen.items()))
+    pa = paralg(Comm())
+    host_m, host_rm, host_cm = pa.paracel_load_as_matrix(str(p), gen_parser(parser_a, ","), "fsmap")
+    rowptr, col, val, rm, cm = pa.paracel_load_as_matrix_device(str(p), gen_parser(parser_a, ","), "fsmap")
+    assert rm.cpu().tolist() == [host_rm[i] for i in range(len(host_rm))]
+    assert cm.cpu().tolist() == [host_cm[i] for i in range(len(host_cm))]
+    dense = np.zeros(host_m.shape)
+    rp = rowptr.cpu().numpy()
+    ri = np.repeat(np.arange(len(rp) - 1), np.diff(rp))
+    dense[ri, col.cpu().numpy()] = val.cpu().numpy()
+    assert np.allclose(dense, host_m.toarray(), atol=1e-6)
