@@ -13,14 +13,17 @@
 // alg/clustering/kmeans/kmeans.hpp:113-133 and the all-pairs products of
 // alg/recommendation/similarity_dense/sim_dense.hpp:84-101.
 //
-// Roles in each CTA (192 threads):
+// Roles in each CTA (320 threads):
 //   warp 0      TMA producer for this CTA's operand halves; the transfers of both
 //               CTAs complete on the LEADER's "full" barrier (cta_group::2 form of
 //               cp.async.bulk.tensor, no multicast)
 //   warp 1      tensor-memory allocation (both CTAs); in the leader one lane issues
 //               the M256 N256 K8 MMAs and commits to the barriers of both CTAs
-//   warps 2-5   epilogue on the CTA's own accumulator half: tcgen05.ld, transpose
-//               through swizzled shared memory, coalesced row stores (or arg-min)
+//   warps 2-9   epilogue on the CTA's own accumulator half, two warps per tensor-memory
+//               sub-partition (each takes 128 of the 256 columns): tcgen05.ld, transpose
+//               through swizzled shared memory, coalesced row stores (or arg-min); the
+//               accumulator buffer is released as soon as its last chunk is in registers.  With K = 512 a tile's MMAs take about 4 us, so four
+//               epilogue warps (about 8 us per tile) were the bottleneck.
 // Every wait has a time limit; on expiry the status record is written, both
 // CTAs of the pair are told to leave, tensor memory is freed and the kernel ends.
 #include <cuda.h>
@@ -38,7 +41,9 @@ constexpr int STAGES = 6;
 constexpr int UMMA_K = 8;
 constexpr int A_BYTES = HM * BK * 4;
 constexpr int B_BYTES = HN * BK * 4;
-constexpr int EPI_BYTES = 4 * 32 * 128;  // one 32 x 32 fp32 chunk per epilogue warp
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
+constexpr int EPI_BYTES = EPI_WARPS * 32 * 128;  // one 32 x 32 fp32 chunk per epilogue warp
 constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr unsigned long long WAIT_NS = 2000000000ull;  // 2 s per wait
 
@@ -152,14 +157,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
         "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
         "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
         "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      : "r"(taddr)
+      : "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
@@ -200,7 +206,7 @@ __device__ __forceinline__ void abort_pair(volatile int* abort_flag, uint32_t pe
                : "memory");
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(THREADS, 1)
 gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      Gemm2Args a) {
   extern __shared__ uint8_t smem_raw[];
@@ -262,13 +268,13 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   uint64_t* full = bars;                 // STAGES, used in the leader
   uint64_t* empty = bars + STAGES;       // STAGES, one set per CTA
   uint64_t* tfull = bars + 2 * STAGES;   // 2, one set per CTA
-  uint64_t* tempty = tfull + 2;          // 2, used in the leader (8 warp arrivals)
+  uint64_t* tempty = tfull + 2;          // 2, used in the leader (one arrival per epilogue warp of the pair)
   uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull + b, 1); mbar_init(tempty + b, 8); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull + b, 1); mbar_init(tempty + b, 2 * EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -397,6 +403,8 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
   } else {
     const int sub = warp & 3;                 // tensor-memory sub-partition of this warp
+    const int half = (warp - 2) >> 2;         // which 128 of the tile's 256 columns
+    constexpr int HC = TN / 2;                // columns per epilogue warp
     float* stg = reinterpret_cast<float*>(sE + (warp - 2) * 4096);
     const uint32_t tempty_leader0 = map_to_cta(smem_u32(tempty), 0);
     int acc = 0;
@@ -424,17 +432,23 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const bool vec_ok = ((a.ldc & 3) == 0) && ((((uintptr_t)a.C) & 15) == 0);
         if (a.epi == 1) {   // |b_n|^2 of this tile's columns, +inf beyond N
           __syncwarp();
-          for (int q = lane; q < TN; q += 32) {
-            const int n = nt * TN + q;
+          for (int q = lane; q < HC; q += 32) {
+            const int n = nt * TN + half * HC + q;
             stg[q] = n < a.N ? __ldg(a.bnorm + n) : 3.402823466e38f;
           }
           __syncwarp();
         }
 #pragma unroll 1
-        for (int c = 0; c < TN / 32; ++c) {
+        for (int c = 0; c < HC / 32; ++c) {
           float v[32];
-          tmem_ld32(t0 + (uint32_t)(c * 32), v);
-          const int n0 = nt * TN + c * 32;
+          tmem_ld32(t0 + (uint32_t)(half * HC + c * 32), v);   // load and wait in one statement
+          if (c + 1 == HC / 32) {
+            // the last chunk is in registers: hand the accumulator buffer back before its stores
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_leader0 + (uint32_t)(acc * 8));
+          }
+          const int n0 = nt * TN + half * HC + c * 32;
           if (n0 >= a.N) continue;
           if (a.epi == 0) {
             if (n0 + 32 <= a.N && vec_ok) {
@@ -488,15 +502,12 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             }
           }
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(tempty_leader0 + (uint32_t)(acc * 8));
         acc_phase[acc] ^= 1;
         acc ^= 1;
       }
-      if (ok && a.epi == 1 && row < a.M) {
-        a.row_min[row] = best;
-        a.row_arg[row] = best_n;
+      if (ok && a.epi == 1 && row < a.M) {   // one result per column half; the caller merges the two
+        a.row_min[(long long)half * a.M + row] = best;
+        a.row_arg[(long long)half * a.M + row] = best_n;
       }
     }
   }
@@ -544,8 +555,10 @@ int make_map2(CUtensorMap* map, const float* ptr, long long rows, long long K, i
 
 }  // namespace
 
-// Same arguments as pcl_gemm_tf32, except that `flags` holds one int per 256-column tile
-// and `gather_ctas` is rounded up to an even number.  Returns cudaErrorNotSupported when the
+// Same arguments as pcl_gemm_tf32, except that `flags` holds one int per 256-column tile,
+// `gather_ctas` is rounded up to an even number, and with epi 1 row_min / row_arg hold 2 x M
+// entries: [0..M) is the result over columns n with (n mod 256) < 128, [M..2M) over the others
+// (the two epilogue warps of a row work on separate column halves; the caller takes the smaller).  Returns cudaErrorNotSupported when the
 // device cannot co-schedule a single pair of CTAs with this much shared memory.
 PCL_API int pcl_gemm_tf32_2sm(const float* A, float* b_stage, float* C, int M, int N, int K,
                               long long ldc, int epi, const float* bnorm, float* row_min, int* row_arg,
@@ -581,7 +594,7 @@ PCL_API int pcl_gemm_tf32_2sm(const float* A, float* b_stage, float* C, int M, i
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cfg.stream = stream;
   cfg.attrs = attr;

@@ -77,6 +77,14 @@ def check_status(device=None) -> None:
                            f"expected {int(host[2])}, saw {int(host[3])}")
 
 
+def _merge_halves(rm2: torch.Tensor, ra2: torch.Tensor):
+    """The two-CTA kernel reports the arg-min per half of the columns of a tile; keep the smaller
+    (the lower column index on ties)."""
+    m0, m1, a0, a1 = rm2[0], rm2[1], ra2[0], ra2[1]
+    take1 = (m1 < m0) | ((m1 == m0) & (a1 < a0))
+    return torch.where(take1, m1, m0), torch.where(take1, a1, a0)
+
+
 def _launch(A, B, C, epi, bnorm, row_min, row_arg, status=None, kernel=None):
     M, K = A.shape
     if status is None:
@@ -116,10 +124,11 @@ def argmin_nt(A: torch.Tensor, B: torch.Tensor, bnorm: Optional[torch.Tensor] = 
         A2, B2 = split3(_pad_k(A), False), split3(_pad_k(B), True)
     else:
         A2, B2 = _pad_k(A), _pad_k(B)
-    row_min = torch.empty(M, device=A.device, dtype=torch.float32)
-    row_arg = torch.empty(M, device=A.device, dtype=torch.int32)
+    two = _entry(kernel) == "pcl_gemm_tf32_2sm"
+    row_min = torch.empty((2, M) if two else (M,), device=A.device, dtype=torch.float32)
+    row_arg = torch.empty((2, M) if two else (M,), device=A.device, dtype=torch.int32)
     _launch(A2, B2, None, 1, bnorm, row_min, row_arg, kernel=kernel)
-    return row_min, row_arg
+    return _merge_halves(row_min, row_arg) if two else (row_min, row_arg)
 
 
 class DenseReadGemm:
@@ -170,12 +179,13 @@ class DenseReadGemm:
                       None, shards, self.flags, self.world, self.rank, self.rps, self.epoch,
                       self.gather_ctas, self.status, 0, _lib.stream_ptr())
             return out
-        row_min = torch.empty(M, device=A.device, dtype=torch.float32)
-        row_arg = torch.empty(M, device=A.device, dtype=torch.int32)
+        two = self.entry == "pcl_gemm_tf32_2sm"
+        row_min = torch.empty((2, M) if two else (M,), device=A.device, dtype=torch.float32)
+        row_arg = torch.empty((2, M) if two else (M,), device=A.device, dtype=torch.int32)
         _lib.call(self.entry, A, stage, None, M, self.N, self.K, 0, 1, argmin_bnorm, row_min,
                   row_arg, shards, self.flags, self.world, self.rank, self.rps, self.epoch,
                   self.gather_ctas, self.status, 0, _lib.stream_ptr())
-        return row_min, row_arg
+        return _merge_halves(row_min, row_arg) if two else (row_min, row_arg)
 
     def check(self):
         st = self.status.cpu()
