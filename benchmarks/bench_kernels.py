@@ -1,0 +1,130 @@
+#!/usr/bin/env python
+"""Micro-benchmarks of the single-GPU algorithm kernels against stock PyTorch ops doing the same
+job: batched ALS solve, k-means accumulate, Gram matrix, device ball-tree search.  CUDA events,
+3 warm-ups, L2 flushed between timed launches, one JSON line per kernel.
+
+    python benchmarks/bench_kernels.py [--kernel als|kmeans|gram|balltree|all]
+"""
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch
+
+
+def timeit(fn, flush, iters=5, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_als(flush):
+    from paracel_b200.ops.als import als_solve
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(1)
+    n_users, n_items, k, per_user = 200_000, 100_000, 128, 100
+    H = torch.randn(n_items, k, device=dev, generator=g) * 0.1
+    ptr = torch.arange(0, n_users * per_user + 1, per_user, device=dev, dtype=torch.int64)
+    idx = torch.randint(0, n_items, (n_users * per_user,), device=dev, generator=g, dtype=torch.int32)
+    r = torch.rand(n_users * per_user, device=dev, generator=g) * 4 + 1
+    ms = timeit(lambda: als_solve(ptr, idx, r, H, 0.1), flush)
+    # stock ops on a slice (the batched Gram build needs n_users x per_user x k floats)
+    nb = 20_000
+
+    def torch_ref():
+        Hu = H[idx[: nb * per_user].long()].view(nb, per_user, k)
+        A = Hu.transpose(1, 2) @ Hu + 0.1 * torch.eye(k, device=dev)
+        b = (Hu * r[: nb * per_user].view(nb, per_user, 1)).sum(1)
+        return torch.linalg.solve(A, b)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ms_ref = timeit(torch_ref, flush) * (n_users / nb)
+    flops = n_users * (2.0 * per_user * k * k + k ** 3 / 3.0 + 2 * k * k)
+    return {"kernel": "als_solve", "users": n_users, "ratings_per_user": per_user, "k": k, "ms": ms,
+            "systems_per_s": n_users / ms * 1e3, "tflops_fp32": flops / ms / 1e9,
+            "torch_gather_bmm_solve_ms_scaled": ms_ref, "speedup": ms_ref / ms}
+
+
+def bench_kmeans(flush):
+    from paracel_b200.ops.misc import kmeans_accumulate
+    dev = "cuda"
+    n, d, k = 4_000_000, 128, 1024
+    X = torch.randn(n, d, device=dev)
+    assign = torch.randint(0, k, (n,), device=dev, dtype=torch.int32)
+    sums = torch.zeros(k, d, device=dev)
+    counts = torch.zeros(k, device=dev)
+
+    def ours():
+        sums.zero_(); counts.zero_()
+        kmeans_accumulate(X, assign, sums, counts)
+
+    def ref():
+        sums.zero_(); counts.zero_()
+        sums.index_add_(0, assign.long(), X)
+        counts.index_add_(0, assign.long(), torch.ones(n, device=dev))
+    ms, ms_ref = timeit(ours, flush), timeit(ref, flush)
+    return {"kernel": "kmeans_accumulate", "n": n, "d": d, "k": k, "ms": ms, "GBps": n * d * 4 / ms / 1e6,
+            "torch_index_add_ms": ms_ref, "speedup": ms_ref / ms}
+
+
+def bench_gram(flush):
+    from paracel_b200.ops.misc import gram
+    dev = "cuda"
+    n, k = 8_000_000, 64
+    H = torch.randn(n, k, device=dev)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ms, ms_ref = timeit(lambda: gram(H), flush), timeit(lambda: H.T @ H, flush)
+    return {"kernel": "gram", "n": n, "k": k, "ms": ms, "GBps": n * k * 4 / ms / 1e6,
+            "torch_fp32_matmul_ms": ms_ref, "speedup": ms_ref / ms}
+
+
+def bench_balltree(flush):
+    import numpy as np
+    from paracel_b200.tool.balltree import DeviceBalltree, PyBalltree, search_batch_gpu
+    rng = np.random.default_rng(0)
+    # clustered items: branch and bound can prune
+    centres = rng.standard_normal((200, 64)) * 4
+    items = (centres[rng.integers(0, 200, 200_000)] + rng.standard_normal((200_000, 64)) * 0.3)
+    tree = PyBalltree(items)
+    tree.build()
+    dt = DeviceBalltree(tree)
+    Q = torch.as_tensor((centres[rng.integers(0, 200, 8192)] + rng.standard_normal((8192, 64)) * 0.3)
+                        .astype(np.float32), device="cuda")
+    ms = timeit(lambda: dt.search(Q, 10), flush)
+    X = dt.items
+
+    def brute():
+        return torch.topk(Q @ X.T, 10, dim=1)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ms_ref = timeit(brute, flush)
+    _, _, vis = dt.search(Q, 10)
+    return {"kernel": "balltree_search", "items": 200_000, "dim": 64, "queries": 8192, "k": 10, "ms": ms,
+            "queries_per_s": 8192 / ms * 1e3, "mean_balls_opened": float(vis.float().mean().item()),
+            "nodes": tree.node_count, "torch_matmul_topk_ms": ms_ref}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="all", choices=["all", "als", "kmeans", "gram", "balltree"])
+    args = ap.parse_args()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    table = {"als": bench_als, "kmeans": bench_kmeans, "gram": bench_gram, "balltree": bench_balltree}
+    for name, fn in table.items():
+        if args.kernel in ("all", name):
+            print(json.dumps(fn(flush)))
+
+
+if __name__ == "__main__":
+    main()

@@ -4,8 +4,8 @@
 // and multiplies by its explicit inverse).  Here one CTA of 256 threads handles one work
 // item = one segment of a user's ratings: the 16 x 16 thread grid keeps the k x k Gram
 // matrix in registers ((k/16)^2 per thread), item rows are staged through shared memory 8 at
-// a time, and the system is solved in shared memory by Cholesky factorisation and two
-// triangular solves.  Users with more ratings than one segment holds are split: every
+// a time, and the system is solved in shared memory by a blocked Cholesky factorisation
+// (16-column panels) and two blocked triangular solves.  Users with more ratings than one segment holds are split: every
 // segment adds its partial Gram matrix and right-hand side into a scratch slot with atomics
 // and the segment that arrives last solves.
 #include "common.cuh"
@@ -30,7 +30,7 @@ struct AlsArgs {
 };
 
 template <int KB>
-__global__ void __launch_bounds__(256) als_kernel(AlsArgs a) {
+__global__ void __launch_bounds__(256, 3) als_kernel(AlsArgs a) {
   constexpr int K = 16 * KB;
   extern __shared__ float sm[];
   float* sA = sm;                       // K x (K + 1)
@@ -106,34 +106,117 @@ __global__ void __launch_bounds__(256) als_kernel(AlsArgs a) {
       }
     if (tid < K) sb[tid] = bacc;
     __syncthreads();
-    // Cholesky A = L L^T in place (lower triangle)
-    for (int j = 0; j < K; ++j) {
-      if (tid == 0) sA[j * (K + 1) + j] = sqrtf(fmaxf(sA[j * (K + 1) + j], 1e-30f));
+    // Blocked Cholesky A = L L^T in place (lower triangle), panels of 16 columns: the 16 x 16
+    // diagonal block is factored by one warp, the rows below are solved one thread per row, and
+    // the trailing matrix gets a rank-16 update with a (KB-1) x (KB-1) register tile per thread.
+    // Three block-wide barriers per panel instead of three per column.
+    constexpr int LD = K + 1;
+    for (int j0 = 0; j0 < K; j0 += 16) {
+      if (tid < 32) {
+        for (int j = 0; j < 16; ++j) {
+          const float d = sqrtf(fmaxf(sA[(j0 + j) * LD + j0 + j], 1e-30f));
+          const float inv = 1.f / d;
+          float lij = 0.f;
+          const bool below = tid < 16 && tid > j;
+          __syncwarp();
+          if (below) {
+            lij = sA[(j0 + tid) * LD + j0 + j] * inv;
+            sA[(j0 + tid) * LD + j0 + j] = lij;
+          }
+          if (tid == j) sA[(j0 + j) * LD + j0 + j] = d;
+          __syncwarp();
+          if (below)
+            for (int c = j + 1; c <= tid; ++c)
+              sA[(j0 + tid) * LD + j0 + c] -= lij * sA[(j0 + c) * LD + j0 + j];
+          __syncwarp();
+        }
+      }
       __syncthreads();
-      const float inv = 1.f / sA[j * (K + 1) + j];
-      for (int i = j + 1 + tid; i < K; i += 256) sA[i * (K + 1) + j] *= inv;
+      const int j1 = j0 + 16;
+      const int m = K - j1;             // rows below the panel
+      if (tid < m) {                    // L21 = A21 L11^-T, one row per thread
+        float* rowp = sA + (j1 + tid) * LD + j0;
+        float x[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float v = rowp[c];
+#pragma unroll
+          for (int q = 0; q < c; ++q) v = fmaf(-x[q], sA[(j0 + c) * LD + j0 + q], v);
+          x[c] = v / sA[(j0 + c) * LD + j0 + c];
+        }
+#pragma unroll
+        for (int c = 0; c < 16; ++c) rowp[c] = x[c];
+      }
       __syncthreads();
-      const int m = K - j - 1;
-      for (int e = tid; e < m * m; e += 256) {
-        const int r = j + 1 + e / m, c = j + 1 + e % m;
-        if (c <= r) sA[r * (K + 1) + c] -= sA[r * (K + 1) + j] * sA[c * (K + 1) + j];
+      if (m > 0) {                      // A22 -= L21 L21^T (lower triangle only)
+        const int mb = m >> 4;
+        float t[KB - 1 > 0 ? KB - 1 : 1][KB - 1 > 0 ? KB - 1 : 1];
+#pragma unroll
+        for (int i = 0; i < KB - 1; ++i)
+#pragma unroll
+          for (int j = 0; j < KB - 1; ++j) t[i][j] = 0.f;
+#pragma unroll 4
+        for (int q = 0; q < 16; ++q) {
+          float lr[KB - 1 > 0 ? KB - 1 : 1], lc[KB - 1 > 0 ? KB - 1 : 1];
+#pragma unroll
+          for (int i = 0; i < KB - 1; ++i) {
+            lr[i] = i < mb ? sA[(j1 + ty + 16 * i) * LD + j0 + q] : 0.f;
+            lc[i] = i < mb ? sA[(j1 + tx + 16 * i) * LD + j0 + q] : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < KB - 1; ++i)
+#pragma unroll
+            for (int j = 0; j < KB - 1; ++j) t[i][j] = fmaf(lr[i], lc[j], t[i][j]);
+        }
+#pragma unroll
+        for (int i = 0; i < KB - 1; ++i)
+#pragma unroll
+          for (int j = 0; j < KB - 1; ++j) {
+            const int r = j1 + ty + 16 * i, c = j1 + tx + 16 * j;
+            if (i < mb && j < mb && c <= r) sA[r * LD + c] -= t[i][j];
+          }
       }
       __syncthreads();
     }
-    // forward: L y = b
-    for (int j = 0; j < K; ++j) {
-      if (tid == 0) sb[j] /= sA[j * (K + 1) + j];
+    // forward: L y = b, panel by panel (a warp solves the 16 x 16 block with shuffles)
+    for (int j0 = 0; j0 < K; j0 += 16) {
+      if (tid < 32) {
+        float bv = tid < 16 ? sb[j0 + tid] : 0.f;
+        for (int c = 0; c < 16; ++c) {
+          const float yc = __shfl_sync(0xffffffffu, bv, c) / sA[(j0 + c) * LD + j0 + c];
+          if (tid == c) bv = yc;
+          else if (tid < 16 && tid > c) bv = fmaf(-sA[(j0 + tid) * LD + j0 + c], yc, bv);
+        }
+        if (tid < 16) sb[j0 + tid] = bv;
+      }
       __syncthreads();
-      const float yj = sb[j];
-      for (int i = j + 1 + tid; i < K; i += 256) sb[i] -= sA[i * (K + 1) + j] * yj;
+      const int j1 = j0 + 16;
+      if (tid < K - j1) {
+        float v = sb[j1 + tid];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) v = fmaf(-sA[(j1 + tid) * LD + j0 + q], sb[j0 + q], v);
+        sb[j1 + tid] = v;
+      }
       __syncthreads();
     }
-    // backward: L^T w = y
-    for (int j = K - 1; j >= 0; --j) {
-      if (tid == 0) sb[j] /= sA[j * (K + 1) + j];
+    // backward: L^T w = y, last panel first
+    for (int j0 = K - 16; j0 >= 0; j0 -= 16) {
+      if (tid < 32) {
+        float bv = tid < 16 ? sb[j0 + tid] : 0.f;
+        for (int c = 15; c >= 0; --c) {
+          const float wc = __shfl_sync(0xffffffffu, bv, c) / sA[(j0 + c) * LD + j0 + c];
+          if (tid == c) bv = wc;
+          else if (tid < c) bv = fmaf(-sA[(j0 + c) * LD + j0 + tid], wc, bv);
+        }
+        if (tid < 16) sb[j0 + tid] = bv;
+      }
       __syncthreads();
-      const float wj = sb[j];
-      for (int i = tid; i < j; i += 256) sb[i] -= sA[j * (K + 1) + i] * wj;
+      if (tid < j0) {
+        float v = sb[tid];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) v = fmaf(-sA[(j0 + q) * LD + tid], sb[j0 + q], v);
+        sb[tid] = v;
+      }
       __syncthreads();
     }
     if (tid < a.k) a.W[(long long)u * a.k + tid] = sb[tid];
@@ -165,7 +248,7 @@ PCL_API int pcl_als_solve(const int* seg_user, const long long* seg_begin, const
   if (k <= 0 || k > 128) return (int)cudaErrorInvalidValue;
   AlsArgs a{seg_user, seg_begin, seg_end, user_nseg, user_slot, item_idx, rating, H, W, scratch,
             slot_count, n_seg, k, lambda};
-  if (blocks <= 0) blocks = 148 * 2;
+  if (blocks <= 0) blocks = 148 * 3;   // three CTAs per SM: the phases of one system are latency bound
   if (n_seg < blocks) blocks = (int)n_seg;
   if (k <= 32) return launch<2>(a, blocks, stream);
   if (k <= 64) return launch<4>(a, blocks, stream);

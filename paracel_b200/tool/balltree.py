@@ -98,7 +98,10 @@ class DeviceBalltree:
         from ..ops import _lib
         if not 1 <= k <= 32:
             raise ValueError("device search supports 1 <= k <= 32")
-        Q = torch.as_tensor(np.asarray(queries, dtype=np.float32), device=self.device).contiguous()
+        if isinstance(queries, torch.Tensor):
+            Q = queries.to(self.device, torch.float32).contiguous()
+        else:
+            Q = torch.as_tensor(np.asarray(queries, dtype=np.float32), device=self.device).contiguous()
         nq = Q.shape[0]
         idx = torch.empty(nq, k, dtype=torch.int64, device=self.device)
         sc = torch.empty(nq, k, dtype=torch.float32, device=self.device)
