@@ -143,3 +143,41 @@ def test_metrics_and_timers(tmp_path):
     t.dump(str(tmp_path / "trace" / "rank0.json"))
     assert json.load(open(str(tmp_path / "trace" / "rank0.json")))["phases"]["pull"]["count"] == 3
     get_logger("t", 0).info("hello")
+
+
+def test_standalone_proxy_collects_two_server_daemons():
+    """The rendezvous proxy as a program: two server daemons report to it, its output is the
+    server_info string a worker is started with."""
+    import socket
+    import subprocess
+    import sys
+    import time
+    from paracel_b200.ps.client import kvclt
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    proxy = subprocess.Popen([sys.executable, "-m", "paracel_b200.launch.proxy", "--nsrv", "2",
+                              "--init_port", str(port), "--host", "127.0.0.1", "--timeout", "60"],
+                             stdout=subprocess.PIPE, env=env, text=True)
+    time.sleep(1.0)
+    servers = [subprocess.Popen([sys.executable, "-m", "paracel_b200.ps.server", "--start_host", "127.0.0.1",
+                                 "--init_port", str(port)], stdout=subprocess.DEVNULL, env=env)
+               for _ in range(2)]
+    try:
+        out, _ = proxy.communicate(timeout=90)
+        eps = [e for e in out.split("_PARACEL_") if e]
+        assert len(eps) == 2 and len(set(eps)) == 2
+        for n, ep in enumerate(eps):
+            host, ports = ep.split(":")
+            c = kvclt(host, int(ports.split(",")[0]), timeout_s=10.0)
+            assert c.push(f"k{n}", n) and c.pull(f"k{n}") == n
+            c.shutdown()
+            c.close()
+        for p in servers:
+            assert p.wait(timeout=30) == 0
+    finally:
+        for p in servers + [proxy]:
+            if p.poll() is None:
+                p.kill()
