@@ -114,10 +114,17 @@ struct SparseGradArgs {
   double* loss;              // accumulated into
 };
 
+// Hot features (ids below hot_T) accumulate per CTA in shared memory as 32-bit fixed point
+// (2^-14 units, native integer atomics: a floating-point shared-memory atomic add is a
+// compare-and-swap loop that retries under contention, and the hottest features are hit by
+// most warps of a CTA at once).  |residual * value| <= a few units and a CTA adds at most a
+// few hundred thousand terms per feature, so 17 integer bits are ample.
+constexpr float SG_FX = 16384.f, SG_FXI = 1.f / 16384.f;
+
 __global__ void __launch_bounds__(256) sparse_grad_kernel(SparseGradArgs a) {
-  extern __shared__ float s_hot[];
+  extern __shared__ int s_hot[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
-  for (int j = threadIdx.x; j < a.hot_T; j += blockDim.x) s_hot[j] = 0.f;
+  for (int j = threadIdx.x; j < a.hot_T; j += blockDim.x) s_hot[j] = 0;
   __syncthreads();
   double loss = 0.0;
   for (long long row = (long long)blockIdx.x * wpb + warp; row < a.n; row += (long long)gridDim.x * wpb) {
@@ -139,17 +146,20 @@ __global__ void __launch_bounds__(256) sparse_grad_kernel(SparseGradArgs a) {
       r = yy - z;
       loss += (double)r * (double)r;
     }
+    // squared-loss residuals are unbounded: keep those in floating point
+    const bool fx_ok = a.logistic != 0;
     for (long long p = b + lane; p < e; p += 32) {
       const int c = a.cols[p];
       const float v = a.vals ? a.vals[p] : 1.f;
-      if (c < a.hot_T) atomicAdd(&s_hot[c], r * v);
-      else atomicAdd(a.g + c, r * v);
+      const float t = r * v;
+      if (c < a.hot_T && fx_ok && fabsf(t) < 64.f) atomicAdd(&s_hot[c], __float2int_rn(t * SG_FX));
+      else atomicAdd(a.g + c, t);
     }
   }
   __syncthreads();
   for (int j = threadIdx.x; j < a.hot_T; j += blockDim.x) {
-    const float v = s_hot[j];
-    if (v != 0.f) atomicAdd(a.g + j, v);
+    const int v = s_hot[j];
+    if (v != 0) atomicAdd(a.g + j, (float)v * SG_FXI);
   }
   if (lane == 0 && loss != 0.0) atomicAdd(a.loss, loss);
 }
