@@ -33,6 +33,7 @@ struct DenseGradArgs {
   double* loss;        // 1, written
   float* scratch;      // gridDim.x * d partial gradients + gridDim.x loss partials (as 2 floats each)
   unsigned int* counter;  // zero before the first launch; the last block resets it
+  int private_acc;     // 1: every warp owns a d-float accumulator in shared memory (no atomics)
 };
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + __expf(-z)); }
@@ -44,10 +45,8 @@ __global__ void __launch_bounds__(256) dense_grad_kernel(DenseGradArgs a) {
   __shared__ double s_loss[8];
   __shared__ int is_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
-  for (int j = threadIdx.x; j < a.d; j += blockDim.x) {
-    s_theta[j] = a.theta[j];
-    s_g[j] = 0.f;
-  }
+  for (int j = threadIdx.x; j < a.d; j += blockDim.x) s_theta[j] = a.theta[j];
+  for (int j = threadIdx.x; j < (a.private_acc ? wpb : 1) * a.d; j += blockDim.x) s_g[j] = 0.f;
   __syncthreads();
   double loss = 0.0;
   for (long long row = (long long)blockIdx.x * wpb + warp; row < a.n; row += (long long)gridDim.x * wpb) {
@@ -67,12 +66,23 @@ __global__ void __launch_bounds__(256) dense_grad_kernel(DenseGradArgs a) {
       r = yy - z;
       loss += (double)r * (double)r;
     }
-    for (int j = lane; j < a.d; j += 32) atomicAdd(&s_g[j], r * x[j]);
+    if (a.private_acc) {
+      // entry j of this warp's accumulator is only ever touched by lane j % 32 of this warp
+      float* gw = s_g + (long long)warp * a.d;
+      for (int j = lane; j < a.d; j += 32) gw[j] = fmaf(r, x[j], gw[j]);
+    } else {
+      for (int j = lane; j < a.d; j += 32) atomicAdd(&s_g[j], r * x[j]);
+    }
   }
   if (lane == 0) s_loss[warp] = loss;  // identical in every lane of the warp
   __syncthreads();
   float* part = a.scratch + (long long)blockIdx.x * a.d;
-  for (int j = threadIdx.x; j < a.d; j += blockDim.x) part[j] = s_g[j];
+  for (int j = threadIdx.x; j < a.d; j += blockDim.x) {
+    float v = s_g[j];
+    if (a.private_acc)
+      for (int w = 1; w < wpb; ++w) v += s_g[(long long)w * a.d + j];
+    part[j] = v;
+  }
   if (threadIdx.x == 0) {
     double l = 0.0;
     for (int w = 0; w < wpb; ++w) l += s_loss[w];
@@ -182,8 +192,10 @@ PCL_API int pcl_lr_dense_grad(const float* X, const float* y, const float* theta
   if (blocks <= 0) blocks = 148 * 2;
   long long need = (n + 7) / 8;
   if (need < blocks) blocks = (int)need;
-  DenseGradArgs a{X, y, theta, n, d, logistic, g, loss, scratch, counter};
-  size_t smem = 2 * (size_t)d * sizeof(float);
+  // per-warp accumulators (8 warps) when they fit into shared memory, else one shared accumulator
+  const int private_acc = (9 * (size_t)d * sizeof(float) <= 200 * 1024) ? 1 : 0;
+  DenseGradArgs a{X, y, theta, n, d, logistic, g, loss, scratch, counter, private_acc};
+  size_t smem = (private_acc ? 9 : 2) * (size_t)d * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(dense_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return (int)e;
@@ -285,8 +297,9 @@ PCL_API int pcl_lr_dense_grad_noalloc(const float* X, const float* y, const floa
   // the partials are fully overwritten by the kernel before they are read
   e = cudaMemsetAsync(slot.counter, 0, sizeof(unsigned int), stream);
   if (e != cudaSuccess) return (int)e;
-  DenseGradArgs a{X, y, theta, n, d, logistic, g, loss, slot.scratch, slot.counter};
-  size_t smem = 2 * (size_t)d * sizeof(float);
+  const int private_acc = (9 * (size_t)d * sizeof(float) <= 200 * 1024) ? 1 : 0;   // as pcl_lr_dense_grad
+  DenseGradArgs a{X, y, theta, n, d, logistic, g, loss, slot.scratch, slot.counter, private_acc};
+  size_t smem = (private_acc ? 9 : 2) * (size_t)d * sizeof(float);
   e = cudaFuncSetAttribute(dense_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dense_grad_kernel<<<blocks, 256, smem, stream>>>(a);
