@@ -1,9 +1,9 @@
 #!/usr/bin/env python
 """Micro-benchmarks of the single-GPU algorithm kernels against stock PyTorch ops doing the same
-job: batched ALS solve, k-means accumulate, Gram matrix, device ball-tree search.  CUDA events,
+job: batched ALS solve, k-means accumulate, Gram matrix, device ball-tree search, dense LR gradient.  CUDA events,
 3 warm-ups, L2 flushed between timed launches, one JSON line per kernel.
 
-    python benchmarks/bench_kernels.py [--kernel als|kmeans|gram|balltree|all]
+    python benchmarks/bench_kernels.py [--kernel als|kmeans|gram|balltree|dense_grad|all]
 """
 import argparse
 import json
@@ -115,12 +115,39 @@ def bench_balltree(flush):
             "nodes": tree.node_count, "torch_matmul_topk_ms": ms_ref}
 
 
+def bench_dense_grad(flush):
+    from paracel_b200.ops.linear import DenseGrad
+    dev = torch.device("cuda")
+    n, d = 2_000_000, 512
+    X = torch.randn(n, d, device=dev)
+    y = (torch.rand(n, device=dev) > 0.5).float()
+    th = torch.randn(d, device=dev) * 0.1
+    g = torch.empty(d, device=dev)
+    dg = DenseGrad(d, dev)
+    ms = timeit(lambda: dg(X, y, th, g), flush)
+
+    def ref():
+        h = torch.sigmoid(X @ th)
+        return X.T @ (y - h)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ms_ref = timeit(ref, flush)
+    peaks = {}
+    pk = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peaks = json.load(open(pk))
+    gbs = n * d * 4 / ms / 1e6
+    return {"kernel": "lr_dense_grad", "n": n, "d": d, "ms": ms, "GBps": gbs,
+            "frac_hbm_of_measured": gbs / peaks.get("hbm_gbs", 6650.0), "torch_two_matvec_ms": ms_ref,
+            "speedup": ms_ref / ms}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="all", choices=["all", "als", "kmeans", "gram", "balltree"])
+    ap.add_argument("--kernel", default="all", choices=["all", "als", "kmeans", "gram", "balltree", "dense_grad"])
     args = ap.parse_args()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    table = {"als": bench_als, "kmeans": bench_kmeans, "gram": bench_gram, "balltree": bench_balltree}
+    table = {"als": bench_als, "kmeans": bench_kmeans, "gram": bench_gram, "balltree": bench_balltree,
+             "dense_grad": bench_dense_grad}
     for name, fn in table.items():
         if args.kernel in ("all", name):
             print(json.dumps(fn(flush)))

@@ -38,6 +38,9 @@ struct DenseGradArgs {
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + __expf(-z)); }
 
+// R > 0: d <= 32 * R, the row and this warp's gradient sums stay in registers (R values per lane,
+// X is read exactly once); R == 0: any d, the row is read twice (the second time from cache).
+template <int R>
 __global__ void __launch_bounds__(256) dense_grad_kernel(DenseGradArgs a) {
   extern __shared__ float sm[];
   float* s_theta = sm;          // d
@@ -49,10 +52,27 @@ __global__ void __launch_bounds__(256) dense_grad_kernel(DenseGradArgs a) {
   for (int j = threadIdx.x; j < (a.private_acc ? wpb : 1) * a.d; j += blockDim.x) s_g[j] = 0.f;
   __syncthreads();
   double loss = 0.0;
+  float gacc[R > 0 ? R : 1];
+#pragma unroll
+  for (int t = 0; t < (R > 0 ? R : 1); ++t) gacc[t] = 0.f;
   for (long long row = (long long)blockIdx.x * wpb + warp; row < a.n; row += (long long)gridDim.x * wpb) {
     const float* x = a.X + row * a.d;
+    float xr[R > 0 ? R : 1];
     float z = 0.f;
-    for (int j = lane; j < a.d; j += 32) z = fmaf(x[j], s_theta[j], z);
+    if constexpr (R > 0) {
+#pragma unroll
+      for (int t = 0; t < R; ++t) {
+        const int j = lane + 32 * t;
+        xr[t] = j < a.d ? __ldg(x + j) : 0.f;
+      }
+#pragma unroll
+      for (int t = 0; t < R; ++t) {
+        const int j = lane + 32 * t;
+        z = fmaf(xr[t], j < a.d ? s_theta[j] : 0.f, z);
+      }
+    } else {
+      for (int j = lane; j < a.d; j += 32) z = fmaf(x[j], s_theta[j], z);
+    }
     z = pcl_warp_sum(z);
     const float yy = a.y[row];
     float r;
@@ -66,12 +86,23 @@ __global__ void __launch_bounds__(256) dense_grad_kernel(DenseGradArgs a) {
       r = yy - z;
       loss += (double)r * (double)r;
     }
-    if (a.private_acc) {
+    if constexpr (R > 0) {
+#pragma unroll
+      for (int t = 0; t < R; ++t) gacc[t] = fmaf(r, xr[t], gacc[t]);
+    } else if (a.private_acc) {
       // entry j of this warp's accumulator is only ever touched by lane j % 32 of this warp
       float* gw = s_g + (long long)warp * a.d;
       for (int j = lane; j < a.d; j += 32) gw[j] = fmaf(r, x[j], gw[j]);
     } else {
       for (int j = lane; j < a.d; j += 32) atomicAdd(&s_g[j], r * x[j]);
+    }
+  }
+  if constexpr (R > 0) {   // registers -> this warp's slot in shared memory
+    float* gw = s_g + (long long)warp * a.d;
+#pragma unroll
+    for (int t = 0; t < R; ++t) {
+      const int j = lane + 32 * t;
+      if (j < a.d) gw[j] = gacc[t];
     }
   }
   if (lane == 0) s_loss[warp] = loss;  // identical in every lane of the warp
@@ -174,6 +205,24 @@ __global__ void __launch_bounds__(256) sparse_grad_kernel(SparseGradArgs a) {
   if (lane == 0 && loss != 0.0) atomicAdd(a.loss, loss);
 }
 
+template <int R>
+int launch_dense_grad_r(const DenseGradArgs& a, int blocks, size_t smem, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(dense_grad_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dense_grad_kernel<R><<<blocks, 256, smem, stream>>>(a);
+  return pcl_last_error();
+}
+
+// rows of up to 1024 floats are kept in registers (needs the per-warp shared-memory slots)
+int launch_dense_grad(const DenseGradArgs& a, int blocks, size_t smem, cudaStream_t stream) {
+  if (a.private_acc && a.d <= 128) return launch_dense_grad_r<4>(a, blocks, smem, stream);
+  if (a.private_acc && a.d <= 256) return launch_dense_grad_r<8>(a, blocks, smem, stream);
+  if (a.private_acc && a.d <= 512) return launch_dense_grad_r<16>(a, blocks, smem, stream);
+  if (a.private_acc && a.d <= 1024) return launch_dense_grad_r<32>(a, blocks, smem, stream);
+  return launch_dense_grad_r<0>(a, blocks, smem, stream);
+}
+
 }  // namespace
 
 // Number of floats of scratch the dense gradient needs for `blocks` blocks and dimension d.
@@ -196,11 +245,7 @@ PCL_API int pcl_lr_dense_grad(const float* X, const float* y, const float* theta
   const int private_acc = (9 * (size_t)d * sizeof(float) <= 200 * 1024) ? 1 : 0;
   DenseGradArgs a{X, y, theta, n, d, logistic, g, loss, scratch, counter, private_acc};
   size_t smem = (private_acc ? 9 : 2) * (size_t)d * sizeof(float);
-  cudaError_t e = cudaFuncSetAttribute(dense_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem);
-  if (e != cudaSuccess) return (int)e;
-  dense_grad_kernel<<<blocks, 256, smem, stream>>>(a);
-  return pcl_last_error();
+  return launch_dense_grad(a, blocks, smem, stream);
 }
 
 PCL_API int pcl_lr_sparse_grad(const long long* row_ptr, const int* cols, const float* vals,
@@ -300,8 +345,5 @@ PCL_API int pcl_lr_dense_grad_noalloc(const float* X, const float* y, const floa
   const int private_acc = (9 * (size_t)d * sizeof(float) <= 200 * 1024) ? 1 : 0;   // as pcl_lr_dense_grad
   DenseGradArgs a{X, y, theta, n, d, logistic, g, loss, slot.scratch, slot.counter, private_acc};
   size_t smem = (private_acc ? 9 : 2) * (size_t)d * sizeof(float);
-  e = cudaFuncSetAttribute(dense_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return (int)e;
-  dense_grad_kernel<<<blocks, 256, smem, stream>>>(a);
-  return pcl_last_error();
+  return launch_dense_grad(a, blocks, smem, stream);
 }

@@ -11,7 +11,7 @@ from . import _lib
 class DenseGrad:
     """g = X^T (y - h(X theta)) and the summed loss for dense fp32 X (row-major)."""
 
-    def __init__(self, d: int, device, blocks: int = 296):
+    def __init__(self, d: int, device, blocks: int = 592):
         self.d, self.blocks = d, blocks
         self.scratch = torch.empty(blocks * d + 2 * blocks + 4, device=device, dtype=torch.float32)
         self.counter = torch.zeros(1, device=device, dtype=torch.int32)
