@@ -41,9 +41,13 @@ def lr_cpu(args):
     np.savetxt(inp, np.concatenate([X, y[:, None]], 1), delimiter=",", fmt="%.6f")
     res = LocalJob(2, 1).run(W.run_lr, (inp, os.path.join(tmp, "out"), "ipm", True, 10), timeout_s=600)
     sec = max(r["seconds"] for r in res)
-    print(json.dumps({"config": "lr_cpu", "metric": "samples/s (LR, CPU plumbing)", "value": n * 10 / sec,
-                      "seconds_10_rounds": sec, "final_logloss": res[0]["loss"], "workers": 2, "servers": 1,
-                      "ssp_staleness": 1, "note": "includes loading/parsing the CSV (solve() wall time)"}))
+    learn = max(r["seconds_learn"] for r in res)
+    print(json.dumps({"config": "lr_cpu", "metric": "samples/s (LR, CPU plumbing)", "value": n * 10 / learn,
+                      "seconds_10_rounds": learn, "seconds_load_and_parse": max(r["seconds_load"] for r in res),
+                      "samples_per_s_including_load": n * 10 / sec, "final_logloss": res[0]["loss"],
+                      "workers": 2, "servers": 1, "ssp_staleness": 1,
+                      "note": "value counts the 10 learning rounds (pull, SGD pass, push, commit); "
+                              "loading and parsing the CSV is reported separately"}))
 
 
 def main():

@@ -153,11 +153,16 @@ class logistic_regression(paralg):
         self._learn("agd")
 
     def solve(self):
+        import time
+        t0 = time.time()
         lines = self.paracel_load(self.input)
         self.local_parser(lines)
         self.paracel_sync()
+        t1 = time.time()
         self._learn(self.learning_method)
         self.paracel_sync()
+        # wall-clock seconds of the two phases (load + parse, learning rounds)
+        self.seconds_load, self.seconds_learn = t1 - t0, time.time() - t1
 
     # ------------------------------------------------------------- metrics
     def calc_loss(self) -> float:

@@ -163,7 +163,8 @@ def run_lr(comm, server_info, inp, out, method, ssp, rounds=10):
     m.predict(inp)
     m.dump_result()
     m.close()
-    return {"loss": loss, "seconds": dt, "n": int(m.samples.shape[0]), "theta": m.theta.tolist()}
+    return {"loss": loss, "seconds": dt, "seconds_learn": m.seconds_learn, "seconds_load": m.seconds_load,
+            "n": int(m.samples.shape[0]), "theta": m.theta.tolist()}
 
 
 def run_wc(comm, server_info, inp, topk, variant="learning"):
