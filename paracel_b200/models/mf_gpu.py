@@ -105,7 +105,7 @@ def grid_rank(u: torch.Tensor, i: torch.Tensor, ugrp: torch.Tensor, igrp: torch.
     gi = igrp[i].to(torch.int64)
     pos = torch.arange(u.numel(), device=u.device, dtype=torch.int64)
     gu = torch.where(gu < 0, pos % npx, gu)
-    gi = torch.where(gi < 0, pos % npy, gi)
+    gi = torch.where(gi < 0, (pos // npx) % npy, gi)   # independent of the row dealt above
     return gu * npy + gi
 
 

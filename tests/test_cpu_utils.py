@@ -282,3 +282,28 @@ def test_type_traits_and_small_helpers():
     assert len(ports) == 2 and all(2014 <= p < 65535 for p in ports)
     with __import__("pytest").raises(RuntimeError):
         misc.ERROR_ABORT("boom")
+
+
+def test_rating_balance_over_the_rank_grid():
+    """balanced_groups + grid_rank: near-equal rating counts per rank for Zipf ids, and an extremely
+    popular item is shared by every column of the grid instead of loading one of them."""
+    import torch
+    from paracel_b200.models.mf_gpu import balanced_groups, grid_rank
+    g = torch.Generator().manual_seed(0)
+    n_u, n_i, nnz = 20000, 4000, 400_000
+    wu = 1.0 / torch.arange(1, n_u + 1, dtype=torch.float64) ** 1.1
+    wi = 1.0 / torch.arange(1, n_i + 1, dtype=torch.float64) ** 1.1
+    u = torch.multinomial(wu, nnz, replacement=True, generator=g)
+    i = torch.multinomial(wi, nnz, replacement=True, generator=g)
+    cu, ci = torch.bincount(u, minlength=n_u), torch.bincount(i, minlength=n_i)
+    for npx, npy in ((2, 4), (2, 2), (1, 2)):
+        ug = balanced_groups(cu, npx, spread_above=0.25)
+        ig = balanced_groups(ci, npy, spread_above=0.25)
+        r = grid_rank(u, i, ug, ig, npx, npy)
+        cnt = torch.bincount(r, minlength=npx * npy).double()
+        assert cnt.max() / cnt.mean() < 1.08, (npx, npy, cnt.tolist())
+        if npy == 4:
+            assert int(ig[0]) == -1                       # the top item is dealt over the columns
+            share = torch.bincount(r[i == 0], minlength=npx * npy).double() / cnt
+            assert share.max() / share.min() < 1.3
+    assert int((balanced_groups(cu, 1) != 0).sum()) == 0
