@@ -602,9 +602,10 @@ class MfSgdGpu:
         return pred
 
     # ------------------------------------------------------------------ dump
-    def dump_result(self, outdir: str):
+    def dump_result(self, outdir: str, user_names=None, item_names=None):
         """Write miu_0, ubias_0, ibias_0, W_0, H_0 in the reference's text layout
-        (mf.hpp:380-492): rank 0 writes what each owner holds, shard by shard."""
+        (mf.hpp:380-492): rank 0 writes what each owner holds, shard by shard.  ``user_names`` /
+        ``item_names`` (arrays indexed by the dense id) give the ids to print."""
         from ..utils.dump import dump_dict_scalar, dump_dict_vector
         os.makedirs(outdir, exist_ok=True)
         self._barrier()
@@ -623,16 +624,19 @@ class MfSgdGpu:
         if self.rank == 0:
             dump_dict_scalar({"miu": self.mu, "rating_sz": float(self.total_nnz)},
                              os.path.join(outdir, "miu_0"))
+            def keys(name, ids):
+                tab = user_names if name in ("ubias_", "W_") else item_names
+                return ids.tolist() if tab is None else [int(tab[j]) for j in ids.tolist()]
             for name in ("ubias_", "ibias_"):
                 with open(os.path.join(outdir, name + "0"), "w") as f:
                     for p in gathered:
                         ids, vals = p[name]
-                        dump_dict_scalar(dict(zip(ids.tolist(), vals.tolist())), f)
+                        dump_dict_scalar(dict(zip(keys(name, ids), vals.tolist())), f)
             for name in ("W_", "H_"):
                 with open(os.path.join(outdir, name + "0"), "w") as f:
                     for p in gathered:
                         ids, vals = p[name]
-                        dump_dict_vector(dict(zip(ids.tolist(), vals.tolist())), f)
+                        dump_dict_vector(dict(zip(keys(name, ids), vals.tolist())), f)
         self._barrier()
 
     def free(self):

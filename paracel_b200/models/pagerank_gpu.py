@@ -118,12 +118,15 @@ class PageRankGpu:
         """Ranks of the owned vertices (vertices without out-links are reported as well)."""
         return self.rank_local[: self.n_local]
 
-    def dump_result(self, outdir: str):
-        """``pagerank_0``: ``vertex\\trank`` for every vertex that has out-links (pr.hpp:184-193)."""
+    def dump_result(self, outdir: str, names=None):
+        """``pagerank_0``: ``vertex\\trank`` for every vertex that has out-links (pr.hpp:184-193);
+        ``names`` (array indexed by the dense vertex id) gives the ids to print."""
         from ..utils.dump import dump_dict_scalar
         os.makedirs(outdir, exist_ok=True)
         self._barrier()
         ids = (torch.nonzero(self.has_out).flatten() + self.lo).cpu().tolist()
+        if names is not None:
+            ids = [int(names[j]) for j in ids]
         vals = self.rank_local[self.has_out].cpu().tolist()
         part = dict(zip(ids, vals))
         parts = [part]

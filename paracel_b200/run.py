@@ -6,6 +6,7 @@ JSON file; the keys accepted here are the ones of the reference drivers."""
 from __future__ import annotations
 
 import argparse
+import os
 import sys
 from typing import Callable, Dict
 
@@ -191,7 +192,13 @@ def main(argv=None) -> int:
     env = main_env()
     try:
         comm = Comm()
-        s = ALGORITHMS[a.algorithm](comm, a.server_info, json_parser(a.cfg_file))
+        driver = ALGORITHMS[a.algorithm]
+        if os.environ.get("PCL_USE_GPU", "0") == "1":     # launcher started with --gpu
+            import torch
+            from .run_gpu import GPU_ALGORITHMS
+            if torch.cuda.is_available() and a.algorithm in GPU_ALGORITHMS:
+                driver = GPU_ALGORITHMS[a.algorithm]
+        s = driver(comm, a.server_info, json_parser(a.cfg_file))
         comm.synchronize()
         closer = getattr(s, "close", None)
         if closer:
