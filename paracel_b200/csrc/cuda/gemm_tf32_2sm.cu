@@ -22,8 +22,9 @@
 //   warps 2-9   epilogue on the CTA's own accumulator half, two warps per tensor-memory
 //               sub-partition (each takes 128 of the 256 columns): tcgen05.ld, transpose
 //               through swizzled shared memory, coalesced row stores (or arg-min); the
-//               accumulator buffer is released as soon as its last chunk is in registers.  With K = 512 a tile's MMAs take about 4 us, so four
-//               epilogue warps (about 8 us per tile) were the bottleneck.
+//               accumulator buffer is released as soon as its last chunk is in registers.
+//               With K = 512 a tile's MMAs take about 4 us; four epilogue warps needed
+//               about 8 us per tile and held the tensor cores back.
 // Every wait has a time limit; on expiry the status record is written, both
 // CTAs of the pair are told to leave, tensor memory is freed and the kernel ends.
 #include <cuda.h>
