@@ -6,9 +6,11 @@ pairs drawn Zipf(1.1), ratings round(clip(p.q + N(0, 0.5), 1, 5)) from rank-16
 latents; model rank 128 fp32, lr 0.005, L2 0.02, SSP staleness 2.  The total
 work is fixed, so the scaling over GPUs is strong scaling.
 
-One step = one training round of the public API (`MfSgdGpu.round`): SSP wait +
-pull of the local rows from the HBM shards, one SGD pass over all local
-ratings, push of the weighted deltas to the owners, clock commit.
+One step = one training round of the public API: `MfSgdGpu` is a `paralg`
+subclass and `round()` is `paracel_read_multi` (SSP wait + pull of the local
+rows from the HBM shards), one SGD pass over all local ratings,
+`paracel_bupdate_multi` (push of the weighted deltas to the owners) and
+`iter_commit`.
 
     python bench.py --gpus 1 --steps 5 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
@@ -17,7 +19,13 @@ ratings, push of the weighted deltas to the owners, clock commit.
 Rank 0 prints one JSON line.  `value` is device-timed (CUDA events, max over
 ranks) with the ratings resident in HBM; `e2e` repeats the measurement with the
 ratings streamed from pinned host memory every round and the round's running
-RMSE read back to the host.
+RMSE read back to the host.  `step_ms` gives the spread of the single steps
+(an event after every step) and `heldout_rmse` the error on 2 M pairs drawn
+from the same distribution that no rank trains on, after all epochs run.
+
+`--impl reference` drives an installed build of the reference (looked up under
+baseline/_ref) through its own executables; when none is installed it prints
+one line saying what is missing.
 """
 from __future__ import annotations
 
@@ -27,9 +35,6 @@ import os
 import sys
 import time
 
-REF_UNAVAILABLE = ("the reference is a CMake C++11 project with no Python packaging "
-                   "(pip: 'neither setup.py nor pyproject.toml found') and needs MPI, ZeroMQ, "
-                   "msgpack-c, Boost, Eigen3, gflags and glog, none of which exist on this image")
 
 
 def parse_args():
@@ -53,20 +58,26 @@ def parse_args():
     ap.add_argument("--phases", action="store_true",
                     help="after the timed steps run two extra rounds with per-phase device timing")
     ap.add_argument("--no-balance", action="store_true")
-    ap.add_argument("--hot-mix", type=float, default=1.0)
+    ap.add_argument("--hot-mix", type=float, default=0.125)
     ap.add_argument("--sgd-blocks", type=int, default=0)
     ap.add_argument("--hot-rows", type=int, default=106)
     ap.add_argument("--variant", type=int, default=0, help="SGD kernel: 0 automatic (16 lanes per rating at rank 128), 1: 32 lanes per rating, "
                          "2: experimental 8 lanes per rating, 3: 16 lanes per rating")
     ap.add_argument("--chunks-per-flush", type=int, default=8)
     ap.add_argument("--zipf-s", type=float, default=1.1)
+    ap.add_argument("--heldout", type=int, default=2_000_000,
+                    help="pairs drawn like the training pairs but never trained on (0: skip)")
+    ap.add_argument("--overlap-push", type=int, default=-1,
+                    help="1: push + commit on a side stream under the next SGD pass; 0: in line; "
+                         "-1: the model's default")
     return ap.parse_args()
 
 
 def main():
     args = parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
+        from benchmarks.reference_arm import run_reference_arm
+        print(json.dumps(run_reference_arm(args)))
         return 0
 
     import torch
@@ -108,6 +119,8 @@ def main():
                   hot_mix=args.hot_mix, sgd_blocks=args.sgd_blocks, device=dev,
                   hot_rows=args.hot_rows, chunks_per_flush=args.chunks_per_flush,
                   variant=args.variant)
+    if args.overlap_push >= 0 and hasattr(model, "overlap_push"):
+        model.overlap_push = bool(args.overlap_push)
 
     # ---- data: every rank regenerates the same global stream and keeps its block
     stream = MfRatingStream(args.users, args.items, args.nnz, s=args.zipf_s, seed=args.seed,
@@ -132,6 +145,19 @@ def main():
     u = torch.cat(us).to(torch.int64)
     i = torch.cat(is_).to(torch.int64)
     r = torch.cat(rs).to(torch.float32)
+    # held-out pairs: one more chunk of the same stream, split evenly over the ranks
+    held = None
+    if args.heldout > 0:
+        hg = torch.Generator(device=dev)
+        hg.manual_seed(args.seed * 1000003 + 999_983)
+        from paracel_b200.utils.synth import zipf_draw
+        hu = zipf_draw(stream.cdf_u, args.heldout, hg)
+        hi = zipf_draw(stream.cdf_i, args.heldout, hg)
+        hr = (stream.P[hu] * stream.Q[hi]).sum(1) + stream.noise * torch.randn(args.heldout, device=dev, generator=hg)
+        hr = torch.round(hr.clamp_(1.0, 5.0))
+        lo_h, hi_h = rank * args.heldout // world, (rank + 1) * args.heldout // world
+        held = (hu[lo_h:hi_h].clone(), hi[lo_h:hi_h].clone(), hr[lo_h:hi_h].clone())
+        del hu, hi, hr
     del us, is_, rs, stream
     local_nnz = u.numel()
     model.load_ratings(u, i, r)
@@ -146,34 +172,55 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    def timed(n_steps, read_result):
+    def heldout_rmse():
+        if held is None or not hasattr(model, "heldout_sse"):
+            return None
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sse, cnt = model.heldout_sse(*held)
+        t = torch.tensor([sse, cnt], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t)
+        barrier()
+        return float((t[0] / t[1].clamp(min=1.0)).sqrt().item())
+
+    def timed(n_steps, read_result):
+        """Total device time of n_steps rounds (max over ranks) and the time of every single
+        step (an event after each one; per step the max over ranks)."""
+        barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(n_steps + 1)]
         l0 = _lib.launches()
-        e0.record()
+        ev[0].record()
         last = None
-        for _ in range(n_steps):
+        for j in range(n_steps):
             model.round()
             if read_result:
                 last = float(model.sse.item())  # device -> host read of the step's result
-        e1.record()
+            ev[j + 1].record()
         torch.cuda.synchronize()
-        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        ms = torch.tensor([ev[0].elapsed_time(ev[-1])] +
+                          [ev[j].elapsed_time(ev[j + 1]) for j in range(n_steps)],
+                          dtype=torch.float64, device=dev)
         barrier()
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item()), _lib.launches() - l0, last
+        steps = sorted(ms[1:].tolist())
+        spread = {"median": steps[len(steps) // 2], "min": steps[0], "max": steps[-1],
+                  "mean": sum(steps) / len(steps)}
+        return float(ms[0].item()), _lib.launches() - l0, last, spread
 
     # ---- device-timed: ratings resident in HBM
     # clocks are sampled every 50 ms from the first warm-up step to the end of the timed steps
     # (a timed region of a few steps can be shorter than one sampling period)
+    rmse0 = heldout_rmse()
     sampler = ClockSampler(local_rank, period_ms=50).start() if rank == 0 else None
     for _ in range(Wm):
         model.round()
-    ms, launches, _ = timed(K, False)
+    ms, launches, _, step_ms = timed(K, False)
     clocks = sampler.stop() if sampler else None
-    model.clock.check()
+    model.paracel_check()
     run_rmse = model.running_rmse()
+    if clocks and clocks.get("sm_mhz"):
+        step_ms["median_ms_x_sm_mhz"] = step_ms["median"] * clocks["sm_mhz"]
     value = args.nnz * K / (ms * 1e-3)
     phases = None
     if args.phases and hasattr(model, "phase_times_ms"):   # extra untimed rounds, diagnostics only
@@ -197,12 +244,14 @@ def main():
         for _ in range(Wm):
             model.round()
             float(model.sse.item())
-        ms2, _, last = timed(K, True)
-        model.clock.check()
+        ms2, _, last, step_ms2 = timed(K, True)
+        model.paracel_check()
         e2e = {"value": args.nnz * K / (ms2 * 1e-3), "unit": "rating updates/s",
-               "ms_per_step": ms2 / K,
+               "ms_per_step": ms2 / K, "step_ms": step_ms2,
                "h2d_bytes_per_step": int(model.h2d_bytes), "d2h_bytes_per_step": 8}
     final_rmse = model.running_rmse()
+    epochs_run = (2 * (K + Wm) if e2e is not None else (K + Wm)) + (2 if phases is not None else 0)
+    rmse1 = heldout_rmse()
 
     factor_mb = ((model.lu.numel() + model.li.numel()) * getattr(model, "D", args.rank) * 4 / 1e6
                  if hasattr(model, "lu") and hasattr(model, "li") else (args.users + args.items) * args.rank * 4 / 1e6 / world)
@@ -240,6 +289,9 @@ def main():
             "clocks": clocks,
             "e2e": e2e,
             "gpu_launches": launches,
+            "step_ms": step_ms,
+            "heldout_rmse": rmse1, "heldout_rmse_initial": rmse0, "heldout_pairs": args.heldout,
+            "epochs_before_heldout_rmse": epochs_run,
             "phases_ms": phases,
             "running_rmse_device_phase": run_rmse,
             "running_rmse_final": final_rmse,

@@ -124,6 +124,23 @@ class MfSgdNcclTorch:
         self._push(self.but, self.plan_u, self.wgt_u * (bu - bu0))
         self._push(self.bit, self.plan_i, self.wgt_i * (bi - bi0))
 
+    def paracel_check(self):
+        return None
+
+    def heldout_sse(self, u, i, r, chunk=1 << 18):
+        """Same contract as ``MfSgdGpu.heldout_sse`` (rows fetched with all_to_all); every rank
+        must call it with the same number of chunks."""
+        dev = self.device
+        u, i, r = u.to(dev, torch.int64), i.to(dev, torch.int64), r.to(dev, torch.float32)
+        sse = torch.zeros((), dtype=torch.float64, device=dev)
+        for s0 in range(0, u.numel(), chunk):
+            pu, pi = self._plan(u[s0:s0 + chunk]), self._plan(i[s0:s0 + chunk])
+            W, H = self._pull(self.Wt, pu), self._pull(self.Ht, pi)
+            bu, bi = self._pull(self.but, pu), self._pull(self.bit, pi)
+            pred = (self.mu + bu + bi + (W * H).sum(1)).clamp_(1.0, 5.0)
+            sse += ((pred - r[s0:s0 + chunk]).double() ** 2).sum()
+        return float(sse.item()), float(u.numel())
+
     def running_rmse(self):
         t = self.sse.clone()
         if self.world > 1:

@@ -123,4 +123,21 @@ __device__ __forceinline__ bool pcl_wait_min_clock(const long long* clocks, int 
   return false;
 }
 
+// A kernel met an id outside its table: record it (first writer wins) so that the host can raise
+// after the stream synchronises.  `where` names the kernel (100 + n), `pos` the position of the id.
+__device__ __forceinline__ void pcl_report_bad_id(PclStatus* st, int rank, int where, long long pos,
+                                                  long long id) {
+  if (st != nullptr && atomicCAS(&st->code, 0, 2) == 0) {
+    st->rank = rank;
+    st->wait_id = where;
+    st->expected = pos;
+    st->seen = id;
+  }
+}
+
+// Current status code as the device sees it (0 when no status block was given).
+__device__ __forceinline__ int pcl_status_code(const PclStatus* st) {
+  return st != nullptr ? *reinterpret_cast<const volatile int*>(&st->code) : 0;
+}
+
 static inline int pcl_last_error() { return (int)cudaGetLastError(); }

@@ -110,12 +110,14 @@ __global__ void __launch_bounds__(256) dense_bupdate_kernel(BupArgs a) {
     if (threadIdx.x == 0)
       ok = pcl_wait_min_clock(a.ready, a.world, a.epoch, a.timeout_ns, a.status, a.rank, 21) ? 1 : 0;
     __syncthreads();
-    if (!ok) return;
   }
+  // After a timed-out wait the block does no work but still takes part in the block count below,
+  // so that the counter is back at zero for the next launch; "done" is then not published.
+  const bool proceed = !(a.ready != nullptr && a.epoch > 0) || ok;
   const long long lo = (long long)a.rank * a.S;
   long long n = a.L - lo;
   if (n > a.S) n = a.S;
-  if (n < 0) n = 0;
+  if (n < 0 || !proceed) n = 0;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nth = (long long)gridDim.x * blockDim.x;
   const bool vec_ok = ((lo & 3) == 0);
@@ -165,11 +167,49 @@ __global__ void __launch_bounds__(256) dense_bupdate_kernel(BupArgs a) {
     const unsigned int prev = atomicAdd(a.block_counter, 1u);
     if (prev == gridDim.x - 1) {
       *a.block_counter = 0u;
-      if (a.done_ptrs != nullptr) {
+      if (a.done_ptrs != nullptr && proceed) {
         __threadfence_system();
         for (int r = 0; r < a.world; ++r) pcl_st_release_sys(a.done_ptrs[r] + a.rank, a.epoch);
       }
     }
+  }
+}
+
+// One-sided update of a dense key: this rank alone adds scale * delta into the owners' shards
+// with vector reductions over NVLink (paracel_update / a bupdate with a linear handler that only
+// one worker issues; include/ps.hpp:689-750).  Nothing waits and nothing is published.
+struct PushDenseArgs {
+  float* const* shards;
+  const float* delta;   // L floats
+  long long L, S;
+  int world, rank;
+  float scale;
+};
+
+__global__ void __launch_bounds__(256) dense_push_kernel(PushDenseArgs a) {
+  const long long nvec = a.L >> 2;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  const long long shift = nvec > 0 ? (((long long)a.rank * a.S) >> 2) % nvec : 0;
+  for (long long v = tid; v < nvec; v += nth) {
+    long long vv = v + shift;            // every rank starts at its own shard
+    if (vv >= nvec) vv -= nvec;
+    const long long e = vv << 2;
+    float4 d = *reinterpret_cast<const float4*>(a.delta + e);
+    d.x *= a.scale; d.y *= a.scale; d.z *= a.scale; d.w *= a.scale;
+    if (d.x == 0.f && d.y == 0.f && d.z == 0.f && d.w == 0.f) continue;
+    int owner = (int)(e / a.S);
+    if (owner >= a.world) owner = a.world - 1;
+    pcl_red_add4_sys(a.shards[owner] + (e - (long long)owner * a.S), d);
+  }
+  for (long long e = (nvec << 2) + tid; e < a.L; e += nth) {
+    const float d = a.delta[e] * a.scale;
+    if (d == 0.f) continue;
+    int owner = (int)(e / a.S);
+    if (owner >= a.world) owner = a.world - 1;
+    asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(a.shards[owner] + (e - (long long)owner * a.S)),
+                 "f"(d)
+                 : "memory");
   }
 }
 
@@ -208,6 +248,19 @@ PCL_API int pcl_dense_bupdate(float* theta, const float* const* deltas, long lon
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 8) blocks = 148 * 8;
   dense_bupdate_kernel<<<(int)blocks, 256, 0, stream>>>(a);
+  return pcl_last_error();
+}
+
+PCL_API int pcl_dense_push(float* const* shards, const float* delta, long long L, long long S,
+                           int world, int rank, float scale, cudaStream_t stream) {
+  if (L <= 0) return 0;
+  if ((S & 3) && world > 1) return (int)cudaErrorInvalidValue;
+  if (reinterpret_cast<uintptr_t>(delta) & 15) return (int)cudaErrorInvalidValue;
+  PushDenseArgs a{shards, delta, L, S, world, rank, scale};
+  long long blocks = (L / 4 + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  dense_push_kernel<<<(int)blocks, 256, 0, stream>>>(a);
   return pcl_last_error();
 }
 

@@ -18,6 +18,7 @@
 #include <stdio.h>
 
 #include "common.cuh"
+#include <mutex>
 #include "pcl_noalloc.h"
 
 namespace {
@@ -287,8 +288,15 @@ struct NoAllocSlot {
   unsigned int* counter = nullptr;
   bool ready = false;
 };
-NoAllocSlot g_noalloc_slots[64];
-char g_noalloc_msg[256] = "";
+NoAllocSlot g_noalloc_slots[64];        // filled under g_noalloc_mutex, one entry per device
+std::mutex g_noalloc_mutex;
+thread_local char g_noalloc_msg[256] = "";   // last message of the calling host thread
+
+int noalloc_fail(cudaError_t e, const char* what) {
+  snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "pcl_lr_dense_grad_noalloc: %s failed: %s", what,
+           cudaGetErrorString(e));
+  return (int)e;
+}
 }  // namespace
 
 PCL_API const char* pcl_lr_dense_grad_noalloc_error() { return g_noalloc_msg; }
@@ -314,12 +322,13 @@ PCL_API int pcl_lr_dense_grad_noalloc(const float* X, const float* y, const floa
   }
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return (int)e;
+  if (e != cudaSuccess) return noalloc_fail(e, "cudaGetDevice");
   if (dev < 0 || dev >= 64) {
     snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "pcl_lr_dense_grad_noalloc: device index %d not supported", dev);
     return (int)cudaErrorInvalidDevice;
   }
   NoAllocSlot& slot = g_noalloc_slots[dev];
+  std::lock_guard<std::mutex> guard(g_noalloc_mutex);   // set-up and launch of one call at a time
   if (!slot.ready) {
     // One-time set-up for this device (it is the current device): translate the symbols
     // into device addresses.  In host code the array names are only stand-ins.
@@ -341,9 +350,11 @@ PCL_API int pcl_lr_dense_grad_noalloc(const float* X, const float* y, const floa
   // the counter must start at zero whatever an earlier (possibly aborted) call left behind;
   // the partials are fully overwritten by the kernel before they are read
   e = cudaMemsetAsync(slot.counter, 0, sizeof(unsigned int), stream);
-  if (e != cudaSuccess) return (int)e;
+  if (e != cudaSuccess) return noalloc_fail(e, "cudaMemsetAsync(counter)");
   const int private_acc = (9 * (size_t)d * sizeof(float) <= 200 * 1024) ? 1 : 0;   // as pcl_lr_dense_grad
   DenseGradArgs a{X, y, theta, n, d, logistic, g, loss, slot.scratch, slot.counter, private_acc};
   size_t smem = (private_acc ? 9 : 2) * (size_t)d * sizeof(float);
-  return launch_dense_grad(a, blocks, smem, stream);
+  const int rc = launch_dense_grad(a, blocks, smem, stream);
+  if (rc != 0) return noalloc_fail((cudaError_t)rc, "kernel launch");
+  return 0;
 }

@@ -37,6 +37,7 @@ struct MfH16Args {
   const unsigned int* packed;
   const int* chdr;
   const float* rtable;
+  const float* hot_fs;   // per hot row: weight of a CTA's delta in the mix (null: flush_scale)
 };
 
 struct Row8 {
@@ -147,7 +148,7 @@ __global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
         float* gp = a.H + idx;           // hot rows are the first T rows of H
         if (it > 0) {
           const int d = hd[idx];
-          if (d != 0) atomicAdd(gp, (float)d * (FX_INV * a.flush_scale));
+          if (d != 0) atomicAdd(gp, (float)d * (FX_INV * (a.hot_fs ? a.hot_fs[idx >> 7] : a.flush_scale)));
         }
         hd[idx] = 0;
         hbase[idx] = __ldcg(gp);
@@ -155,7 +156,7 @@ __global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
       for (int row = threadIdx.x; row < T; row += blockDim.x) {
         if (it > 0) {
           const int d = hbd[row];
-          if (d != 0) atomicAdd(a.bi + row, (float)d * (FX_INV * a.flush_scale));
+          if (d != 0) atomicAdd(a.bi + row, (float)d * (FX_INV * (a.hot_fs ? a.hot_fs[row] : a.flush_scale)));
         }
         hbd[row] = 0;
         hbb[row] = __ldcg(a.bi + row);
@@ -276,11 +277,11 @@ __global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
     __syncthreads();
     for (int idx = threadIdx.x; idx < T * D; idx += blockDim.x) {
       const int d = hd[idx];
-      if (d != 0) atomicAdd(a.H + idx, (float)d * (FX_INV * a.flush_scale));
+      if (d != 0) atomicAdd(a.H + idx, (float)d * (FX_INV * (a.hot_fs ? a.hot_fs[idx >> 7] : a.flush_scale)));
     }
     for (int row = threadIdx.x; row < T; row += blockDim.x) {
       const int d = hbd[row];
-      if (d != 0) atomicAdd(a.bi + row, (float)d * (FX_INV * a.flush_scale));
+      if (d != 0) atomicAdd(a.bi + row, (float)d * (FX_INV * (a.hot_fs ? a.hot_fs[row] : a.flush_scale)));
     }
   }
   if (a.sse != nullptr && l == 0 && sse != 0.f) atomicAdd(a.sse, (double)sse);
@@ -291,14 +292,14 @@ __global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
 // Same contract as pcl_mf_sgd_pass (mf.cu) for D = 128: user-major sorted ratings in chunks of
 // 32, plain (ru, ri, rr) or compact (packed, chdr, rtable) stream, hot item rows (local index
 // below hot_T) replicated in shared memory and mixed every `cpw` chunks per half-warp with
-// weight `flush_scale` (<= 0: 1 / blocks).  `blocks` <= 0 selects one CTA per SM; `threads` is 512, 640 (default), 768 or 1024
+// weight `flush_scale` (<= 0: 1 / blocks) or, when `hot_fs` is given, with one weight per hot row.  `blocks` <= 0 selects one CTA per SM; `threads` is 512, 640 (default), 768 or 1024
 // (threads / 16 chunks in flight per CTA).
 PCL_API int pcl_mf_sgd_pass_h16(const int* ru, const int* ri, const float* rr, long long nnz,
                                 float* W, float* H, float* bu, float* bi, const float* su,
                                 const float* si, float mu, float alpha, float beta, int hot_T,
                                 int cpw, float flush_scale, int blocks, double* sse,
                                 const unsigned int* packed, const int* chdr, const float* rtable,
-                                int threads, cudaStream_t stream) {
+                                int threads, const float* hot_fs, cudaStream_t stream) {
   if (nnz <= 0) return 0;
   if (nnz % 32 != 0 || hot_T < 0) return (int)cudaErrorInvalidValue;
   if (packed != nullptr && (chdr == nullptr || rtable == nullptr)) return (int)cudaErrorInvalidValue;
@@ -313,6 +314,7 @@ PCL_API int pcl_mf_sgd_pass_h16(const int* ru, const int* ri, const float* rr, l
   a.hot_T = hot_T;
   a.cpw = cpw > 0 ? cpw : 8;
   a.packed = packed; a.chdr = chdr; a.rtable = rtable;
+  a.hot_fs = hot_fs;
   if (threads <= 0) threads = 640;   // 20 warps = 40 chunks in flight per CTA
   if (threads != 512 && threads != 640 && threads != 768 && threads != 1024) return (int)cudaErrorInvalidValue;
   if (blocks <= 0) blocks = 148;

@@ -188,3 +188,36 @@ PCL_API int pcl_allreduce_sum_f64(const double* in, double* out, int n, double* 
   allreduce_sum_kernel<<<1, 256, 0, stream>>>(a);
   return pcl_last_error();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Range check of an id array that a later kernel will use as an index without looking at it
+// again (rating streams, CSR column arrays, word ids, topic assignments): run once when the
+// data is loaded.  The first id outside [lo, hi) is recorded in the status block (code 2,
+// wait_id 110, expected = position, seen = id); `skip` is a value that is allowed although it
+// is out of range (padding markers), pass lo to allow none.
+namespace {
+template <typename T>
+__global__ void validate_ids_kernel(const T* ids, long long n, long long lo, long long hi,
+                                    long long skip, PclStatus* st, int rank) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long g = (long long)ids[i];
+    if ((g < lo || g >= hi) && g != skip) pcl_report_bad_id(st, rank, 110, i, g);
+  }
+}
+}  // namespace
+
+PCL_API int pcl_validate_ids(const void* ids, int is64, long long n, long long lo, long long hi,
+                             long long skip, PclStatus* status, int rank, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (status == nullptr) return (int)cudaErrorInvalidValue;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (is64)
+    validate_ids_kernel<long long><<<(int)blocks, 256, 0, stream>>>(
+        static_cast<const long long*>(ids), n, lo, hi, skip, status, rank);
+  else
+    validate_ids_kernel<int><<<(int)blocks, 256, 0, stream>>>(static_cast<const int*>(ids), n, lo,
+                                                              hi, skip, status, rank);
+  return pcl_last_error();
+}

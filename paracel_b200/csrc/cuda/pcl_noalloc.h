@@ -30,6 +30,17 @@
 //     itself.  Two calls whose kernels can overlap on the GPU (different
 //     streams without an ordering between them) race on the array: order them.
 //   * The function calls no cudaMalloc, cudaFree or other allocating routine.
+//     The 4 MiB themselves are taken by the CUDA runtime when it loads this
+//     library's device code on a GPU; with lazy module loading that can be as
+//     late as the first call on that GPU (or any earlier kernel of this
+//     library there).  An embedder that hands the rest of the memory to an
+//     arena should make that first call before it sizes the arena.
+//   * Host threads: calls from several host threads are serialised by a lock
+//     inside the function (set-up and launch), so threads that drive different
+//     devices may call at the same time; pcl_lr_dense_grad_noalloc_error()
+//     returns the message of the calling thread's own last call.  Every
+//     non-zero return code leaves a message.  The rule on overlapping kernels
+//     of one device above still holds between threads.
 #pragma once
 #include <cuda_runtime.h>
 

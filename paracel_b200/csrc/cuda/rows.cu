@@ -15,7 +15,7 @@
 
 namespace {
 
-enum Handler { H_ADD = 0, H_SCALED_ADD = 1, H_MAX = 2 };
+enum Handler { H_ADD = 0, H_SCALED_ADD = 1, H_MAX = 2, H_ASSIGN = 3 };
 
 struct PullArgs {
   const long long* ids;      // n global row ids
@@ -30,6 +30,7 @@ struct PullArgs {
   unsigned long long timeout_ns;
   PclStatus* status;
   int rank;
+  long long rows;            // table extent: ids outside [0, rows) are reported and skipped
 };
 
 __global__ void __launch_bounds__(256) rows_pull_kernel(PullArgs a) {
@@ -51,6 +52,10 @@ __global__ void __launch_bounds__(256) rows_pull_kernel(PullArgs a) {
   for (long long row = (long long)blockIdx.x * rows_per_block + rib; row < a.n;
        row += (long long)gridDim.x * rows_per_block) {
     long long g = a.ids[row];
+    if (g < 0 || g >= a.rows) {
+      if (sub == 0) pcl_report_bad_id(a.status, a.rank, 101, row, g);
+      continue;
+    }
     int owner = (int)(g % a.world);
     long long lrow = g / a.world;
     const float* src = a.shards[owner] + lrow * a.D;
@@ -77,15 +82,29 @@ struct PushArgs {
   int handler;
   int refresh_old;     // write old = cur after pushing
   long long start;     // rows are visited in the order start, start+1, .., n-1, 0, .., start-1
+  long long rows;      // table extent
+  PclStatus* status;   // bad ids are reported here; a non-zero code on entry cancels the push
+  int rank;
 };
 
+// Maximum handler on a row that may live in a peer GPU: system-scope integer atomics on the
+// order-preserving bit pattern.  Precondition: neither value is NaN.  -0.0f is stored as +0.0f
+// so that the signed / unsigned comparison orders the two zeros consistently.
 __device__ __forceinline__ void atomic_max_f32(float* p, float v) {
-  // order-preserving integer trick; valid for non-NaN values
-  if (v >= 0.f) atomicMax(reinterpret_cast<int*>(p), __float_as_int(v));
-  else atomicMin(reinterpret_cast<unsigned int*>(p), __float_as_uint(v));
+  if (v == 0.f) v = 0.f;
+  if (v >= 0.f) atomicMax_system(reinterpret_cast<int*>(p), __float_as_int(v));
+  else atomicMin_system(reinterpret_cast<unsigned int*>(p), __float_as_uint(v));
+}
+
+__device__ __forceinline__ void st_sys4(float* p, float4 v) {
+  asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y),
+               "f"(v.z), "f"(v.w)
+               : "memory");
 }
 
 __global__ void __launch_bounds__(256) rows_push_kernel(PushArgs a) {
+  // a wait of this round that timed out (or a bad id) left the working copies stale: push nothing
+  if (pcl_status_code(a.status) != 0) return;
   const int vec_per_row = a.D >> 2;
   int tpr = 32;
   while (tpr > vec_per_row) tpr >>= 1;
@@ -100,6 +119,10 @@ __global__ void __launch_bounds__(256) rows_push_kernel(PushArgs a) {
     long long row = it + a.start;
     if (row >= a.n) row -= a.n;
     long long g = a.ids[row];
+    if (g < 0 || g >= a.rows) {
+      if (sub == 0) pcl_report_bad_id(a.status, a.rank, 102, row, g);
+      continue;
+    }
     int owner = (int)(g % a.world);
     long long lrow = g / a.world;
     float* dstp = a.shards[owner] + lrow * a.D;
@@ -119,6 +142,8 @@ __global__ void __launch_bounds__(256) rows_push_kernel(PushArgs a) {
         atomic_max_f32(dstp + 4 * v + 1, x.y);
         atomic_max_f32(dstp + 4 * v + 2, x.z);
         atomic_max_f32(dstp + 4 * v + 3, x.w);
+      } else if (a.handler == H_ASSIGN) {
+        st_sys4(dstp + 4 * v, x);
       } else {
         d.x *= w; d.y *= w; d.z *= w; d.w *= w;
         if (d.x != 0.f || d.y != 0.f || d.z != 0.f || d.w != 0.f)
@@ -152,12 +177,20 @@ struct ScalarArgs {
   float* old;
   const float* wgt;
   int refresh_old;
+  int handler;
+  long long rows;
+  PclStatus* status;
+  int rank;
 };
 
 __global__ void scalars_pull_kernel(ScalarArgs a) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n;
        i += (long long)gridDim.x * blockDim.x) {
     long long g = a.ids[i];
+    if (g < 0 || g >= a.rows) {
+      pcl_report_bad_id(a.status, a.rank, 103, i, g);
+      continue;
+    }
     const float* src = a.shards[(int)(g % a.world)] + g / a.world;
     float x;
     asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(x) : "l"(src));
@@ -167,11 +200,24 @@ __global__ void scalars_pull_kernel(ScalarArgs a) {
 }
 
 __global__ void scalars_push_kernel(ScalarArgs a) {
+  if (pcl_status_code(a.status) != 0) return;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n;
        i += (long long)gridDim.x * blockDim.x) {
     long long g = a.ids[i];
+    if (g < 0 || g >= a.rows) {
+      pcl_report_bad_id(a.status, a.rank, 104, i, g);
+      continue;
+    }
     float* dstp = a.shards[(int)(g % a.world)] + g / a.world;
     float x = a.cur[i];
+    if (a.handler == H_MAX) {
+      atomic_max_f32(dstp, x);
+      continue;
+    }
+    if (a.handler == H_ASSIGN) {
+      asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(dstp), "f"(x) : "memory");
+      continue;
+    }
     float d = a.old ? x - a.old[i] : x;
     if (a.wgt) d *= a.wgt[i];
     if (d != 0.f)
@@ -194,6 +240,9 @@ struct IRowArgs {
   int* cur;
   int* old;
   int refresh_old;
+  long long rows;
+  PclStatus* status;
+  int rank;
 };
 
 __global__ void __launch_bounds__(256) irows_pull_kernel(IRowArgs a) {
@@ -202,6 +251,10 @@ __global__ void __launch_bounds__(256) irows_pull_kernel(IRowArgs a) {
   for (long long row = (long long)blockIdx.x * wpb + warp; row < a.n;
        row += (long long)gridDim.x * wpb) {
     long long g = a.ids[row];
+    if (g < 0 || g >= a.rows) {
+      if (lane == 0) pcl_report_bad_id(a.status, a.rank, 105, row, g);
+      continue;
+    }
     const int* src = a.shards[(int)(g % a.world)] + (g / a.world) * a.D;
     for (int v = lane; v < vec_per_row; v += 32) {
       int4 x;
@@ -215,10 +268,15 @@ __global__ void __launch_bounds__(256) irows_pull_kernel(IRowArgs a) {
 }
 
 __global__ void __launch_bounds__(256) irows_push_kernel(IRowArgs a) {
+  if (pcl_status_code(a.status) != 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   for (long long row = (long long)blockIdx.x * wpb + warp; row < a.n;
        row += (long long)gridDim.x * wpb) {
     long long g = a.ids[row];
+    if (g < 0 || g >= a.rows) {
+      if (lane == 0) pcl_report_bad_id(a.status, a.rank, 106, row, g);
+      continue;
+    }
     int* dstp = a.shards[(int)(g % a.world)] + (g / a.world) * a.D;
     for (int e = lane; e < a.D; e += 32) {
       int x = a.cur[row * a.D + e];
@@ -247,10 +305,10 @@ inline int grid_for(long long work_items, int per_block, int max_blocks) {
 PCL_API int pcl_rows_pull_f32(const long long* ids, float* const* shards, int world, int D,
                               long long n, float* dst, float* dst0, const long long* clocks,
                               long long target, unsigned long long timeout_ns,
-                              PclStatus* status, int rank, cudaStream_t stream) {
+                              PclStatus* status, int rank, long long rows, cudaStream_t stream) {
   if (D <= 0 || (D & 3)) return (int)cudaErrorInvalidValue;
   if (n <= 0 && !(clocks && target > 0)) return 0;
-  PullArgs a{ids, shards, world, D, n, dst, dst0, clocks, target, timeout_ns, status, rank};
+  PullArgs a{ids, shards, world, D, n, dst, dst0, clocks, target, timeout_ns, status, rank, rows};
   int vec = D >> 2, tpr = 32;
   while (tpr > vec) tpr >>= 1;
   int grid = grid_for(n, 256 / tpr, 148 * 16);
@@ -261,11 +319,12 @@ PCL_API int pcl_rows_pull_f32(const long long* ids, float* const* shards, int wo
 PCL_API int pcl_rows_push_f32(const long long* ids, float* const* shards, int world, int D,
                               long long n, float* cur, float* old, const float* wgt,
                               float scale, int handler, int refresh_old, long long start,
-                              cudaStream_t stream) {
+                              long long rows, PclStatus* status, int rank, cudaStream_t stream) {
   if (D <= 0 || (D & 3)) return (int)cudaErrorInvalidValue;
   if (n <= 0) return 0;
   if (start < 0 || start >= n) start = 0;
-  PushArgs a{ids, shards, world, D, n, cur, old, wgt, scale, handler, refresh_old, start};
+  PushArgs a{ids, shards, world, D, n, cur, old, wgt, scale, handler, refresh_old, start,
+             rows, status, rank};
   int vec = D >> 2, tpr = 32;
   while (tpr > vec) tpr >>= 1;
   int grid = grid_for(n, 256 / tpr, 148 * 16);
@@ -274,37 +333,40 @@ PCL_API int pcl_rows_push_f32(const long long* ids, float* const* shards, int wo
 }
 
 PCL_API int pcl_scalars_pull_f32(const long long* ids, float* const* shards, int world,
-                                 long long n, float* cur, float* old, cudaStream_t stream) {
+                                 long long n, float* cur, float* old, long long rows,
+                                 PclStatus* status, int rank, cudaStream_t stream) {
   if (n <= 0) return 0;
-  ScalarArgs a{ids, shards, world, n, cur, old, nullptr, 0};
+  ScalarArgs a{ids, shards, world, n, cur, old, nullptr, 0, H_ADD, rows, status, rank};
   scalars_pull_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, stream>>>(a);
   return pcl_last_error();
 }
 
 PCL_API int pcl_scalars_push_f32(const long long* ids, float* const* shards, int world,
                                  long long n, float* cur, float* old, const float* wgt,
-                                 int refresh_old, cudaStream_t stream) {
+                                 int refresh_old, int handler, long long rows, PclStatus* status,
+                                 int rank, cudaStream_t stream) {
   if (n <= 0) return 0;
-  ScalarArgs a{ids, shards, world, n, cur, old, wgt, refresh_old};
+  ScalarArgs a{ids, shards, world, n, cur, old, wgt, refresh_old, handler, rows, status, rank};
   scalars_push_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, stream>>>(a);
   return pcl_last_error();
 }
 
 PCL_API int pcl_rows_pull_i32(const long long* ids, int* const* shards, int world, int D,
-                              long long n, int* cur, int* old, cudaStream_t stream) {
+                              long long n, int* cur, int* old, long long rows, PclStatus* status,
+                              int rank, cudaStream_t stream) {
   if (D <= 0 || (D & 3)) return (int)cudaErrorInvalidValue;
   if (n <= 0) return 0;
-  IRowArgs a{ids, shards, world, D, n, cur, old, 0};
+  IRowArgs a{ids, shards, world, D, n, cur, old, 0, rows, status, rank};
   irows_pull_kernel<<<grid_for(n, 8, 148 * 16), 256, 0, stream>>>(a);
   return pcl_last_error();
 }
 
 PCL_API int pcl_rows_push_i32(const long long* ids, int* const* shards, int world, int D,
-                              long long n, int* cur, int* old, int refresh_old,
-                              cudaStream_t stream) {
+                              long long n, int* cur, int* old, int refresh_old, long long rows,
+                              PclStatus* status, int rank, cudaStream_t stream) {
   if (D <= 0 || (D & 3)) return (int)cudaErrorInvalidValue;
   if (n <= 0) return 0;
-  IRowArgs a{ids, shards, world, D, n, cur, old, refresh_old};
+  IRowArgs a{ids, shards, world, D, n, cur, old, refresh_old, rows, status, rank};
   irows_push_kernel<<<grid_for(n, 8, 148 * 16), 256, 0, stream>>>(a);
   return pcl_last_error();
 }

@@ -16,7 +16,9 @@
 namespace {
 
 __global__ void ssp_commit_kernel(long long* const* clock_ptrs, int world, int rank,
-                                  long long value) {
+                                  long long value, const PclStatus* status) {
+  // a rank whose wait ran out (or that met a bad id) this round does not announce progress
+  if (pcl_status_code(status) != 0) return;
   int r = threadIdx.x;
   if (r < world) {
     __threadfence_system();  // order this rank's earlier pushes before the clock
@@ -33,9 +35,10 @@ __global__ void ssp_wait_kernel(const long long* clocks, int world, long long ta
 }  // namespace
 
 PCL_API int pcl_ssp_commit(long long* const* clock_ptrs, int world, int rank, long long value,
-                           cudaStream_t stream) {
+                           const PclStatus* status, cudaStream_t stream) {
   if (world > 1024) return (int)cudaErrorInvalidValue;
-  ssp_commit_kernel<<<1, ((world + 31) / 32) * 32, 0, stream>>>(clock_ptrs, world, rank, value);
+  ssp_commit_kernel<<<1, ((world + 31) / 32) * 32, 0, stream>>>(clock_ptrs, world, rank, value,
+                                                                status);
   return pcl_last_error();
 }
 

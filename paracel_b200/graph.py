@@ -66,8 +66,11 @@ class _AdjGraph:
                 func(v, w, wgt)
 
     def traverse_by_vertex(self, func: Callable) -> None:
-        for v in self.adj.items():
-            func(v)
+        """Call ``func((vertex, {neighbour: weight}))`` once per vertex: like the reference, which
+        hands ``func`` the ``std::pair`` of its adjacency map (graph.hpp:104-108, 255-259), the
+        argument is the (vertex, adjacency) pair, not the bare vertex."""
+        for item in self.adj.items():
+            func(item)
 
     def v(self) -> int:
         return len(self.adj)

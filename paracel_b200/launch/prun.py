@@ -57,7 +57,13 @@ def build_parser() -> argparse.ArgumentParser:
 
 
 def _log_cmd(cmd: List[str]) -> None:
-    with open("paracelrun_log", "a") as f:
+    """Append the command line to the run log (the reference's prun.py writes ``paracelrun_log``
+    in the working directory).  ``PARACEL_RUN_LOG`` names another file; an empty value
+    switches the log off."""
+    path = os.environ.get("PARACEL_RUN_LOG", "paracelrun_log")
+    if not path:
+        return
+    with open(path, "a") as f:
         f.write(" ".join(cmd) + "\n")
 
 

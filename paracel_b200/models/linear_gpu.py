@@ -2,16 +2,21 @@
 reference's logistic / ridge regression, alg/classification/logistic_regression/lr.cpp, and
 the parameter-server form of its serial L1 tools, tool/lr_l1_serial.cpp, tool/lasso_serial.cpp).
 
-One step is the reference's "dgd" round (lr.cpp:119-145) on a minibatch:
+Both classes are ``paralg`` subclasses on the device backend; the weights are the dense key
+``"theta"``.  One step is the reference's "dgd" round (lr.cpp:119-145) on a minibatch:
 
-    theta = paracel_read("theta")            -> DenseTable.read    (all-gather by peer loads)
-    g     = sum_rows (y - h(theta.x)) x      -> dense / sparse gradient kernel, written into
-                                                 the table's delta buffer
-    paracel_bupdate("theta", g)              -> DenseTable.bupdate (reduce-scatter fused with the
-                                                 registered handler)
+    theta = paracel_read("theta")            all-gather of the shards by peer loads
+    g     = sum_rows (y - h(theta.x)) x      dense / sparse gradient kernel, written into
+                                             paracel_delta_buffer("theta")
+    paracel_bupdate("theta", g, "", handler, collective=True)
+                                             reduce-scatter fused with the handler at the owner
 
 with handler ``sgd`` (plain step), ``prox_l1`` (proximal gradient: soft threshold with
 lambda -- sparse L1 logistic regression / Lasso) or ridge's shrinkage folded into the step.
+``DenseLinearGpu`` also has the reference's asynchronous methods (lr.cpp:154-299): ``ipm``
+(local SGD pass, then one update with the mean of the workers' moves), ``downpour`` and ``agd``
+(local SGD with one-sided pushes of the accumulated move and periodic re-reads), whose updates
+are one-sided reductions into the owners' HBM (``paracel_update``).
 """
 from __future__ import annotations
 
@@ -21,8 +26,9 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
+from ..ops import _lib
 from ..ops.linear import DenseGrad, sparse_grad
-from ..ps.tables import DenseTable
+from ..paralg import paralg
 
 
 def remap_by_frequency(cols: torch.Tensor, n_features: int):
@@ -35,15 +41,17 @@ def remap_by_frequency(cols: torch.Tensor, n_features: int):
     return inv[cols.long()].to(torch.int32), order
 
 
-class SparseLinearGpu:
+class SparseLinearGpu(paralg):
     def __init__(self, n_features: int, eta: float = 0.5, lam: float = 1e-6, logistic: bool = True,
-                 l1: bool = True, group=None, device=None, hot_T: int = 8192, nbatch: int = 1):
+                 l1: bool = True, group=None, device=None, hot_T: int = 8192, nbatch: int = 1,
+                 comm=None, hosts_dct_str=None, output: str = ""):
+        super().__init__(hosts_dct_str, comm, output, backend="gpu", device=device, group=group)
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world, self.rank = self.get_worker_size(), self.get_worker_id()
         self.F, self.eta, self.lam, self.logistic = int(n_features), float(eta), float(lam), logistic
-        self.table = DenseTable(self.F, group, device, handler="prox_l1" if l1 else "sgd")
-        self.device = self.table.device
+        self.handler = "prox_l1" if l1 else "sgd"
+        self.table = self.paracel_dense_table("theta", self.F, handler=self.handler).table
+        self.table.count_nnz = True
         self.hot_T, self.nbatch = hot_T, max(1, int(nbatch))
         self.loss = torch.zeros(1, dtype=torch.float64, device=self.device)
         self.step_no = 0
@@ -64,14 +72,16 @@ class SparseLinearGpu:
         # minibatch boundaries in rows
         b = torch.linspace(0, self.n_local, self.nbatch + 1).long().tolist()
         self.batches = [(b[i], b[i + 1]) for i in range(self.nbatch)]
-        self.table.write(torch.zeros(self.F, device=dev))
+        # the gradient kernel indexes theta with these column ids: check them once
+        _lib.validate_ids(self.cols, 0, self.F, "sparse linear model (feature ids)")
+        self.paracel_write("theta", torch.zeros(self.F, device=dev))
 
     def step(self):
         """One minibatch step on every rank; returns nothing (loss stays on the device)."""
         lo, hi = self.batches[self.step_no % self.nbatch]
         self.step_no += 1
-        theta = self.table.read()
-        delta = self.table.delta()
+        theta = self.paracel_read("theta")
+        delta = self.paracel_delta_buffer("theta")
         delta.zero_()
         self.loss.zero_()
         if hi > lo:
@@ -80,11 +90,20 @@ class SparseLinearGpu:
             sparse_grad(base, self.cols, self.vals, self.y[lo:hi], theta, delta, self.loss,
                         self.logistic, self.hot_T)
         nb = self.n_total / self.nbatch
-        self.table.bupdate(lr=-self.eta / nb, lam=self.lam, count_nnz=True)
+        self.paracel_bupdate("theta", delta, "", self.handler, collective=True, lr=-self.eta / nb,
+                             lam=self.lam)
 
     def epoch(self):
-        for _ in range(self.nbatch):
-            self.step()
+        with self.phase("epoch"):
+            for _ in range(self.nbatch):
+                self.step()
+        self.log_metrics(step=self.step_no, samples=self.n_local)
+
+    def checkpoint_extra(self):
+        return {"step_no": self.step_no}
+
+    def restore_extra(self, extra):
+        self.step_no = int(extra["step_no"])
 
     def mean_loss(self) -> float:
         """Mean loss of the last step's minibatch (before that step's update), all ranks."""
@@ -100,24 +119,23 @@ class SparseLinearGpu:
         return int(t.item())
 
     def weights(self) -> torch.Tensor:
-        return self.table.read().clone()
+        return self.paracel_read("theta").clone()
 
     def free(self):
-        torch.cuda.synchronize(self.device)
-        self.table.free()
+        self.table = None
+        self.close()
 
 
-class DenseLinearGpu:
+class DenseLinearGpu(paralg):
     """Dense logistic / ridge regression, one ``dgd`` round per step."""
 
     def __init__(self, dim: int, eta: float = 0.1, beta: float = 0.0, logistic: bool = True,
-                 group=None, device=None):
+                 group=None, device=None, comm=None, hosts_dct_str=None, output: str = ""):
+        super().__init__(hosts_dct_str, comm, output, backend="gpu", device=device, group=group)
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world, self.rank = self.get_worker_size(), self.get_worker_id()
         self.d, self.eta, self.beta, self.logistic = int(dim), float(eta), float(beta), logistic
-        self.table = DenseTable(self.d, group, device, handler="sgd")
-        self.device = self.table.device
+        self.table = self.paracel_dense_table("theta", self.d, handler="sgd").table
         self.grad = DenseGrad(self.d, self.device)
 
     def load(self, X: torch.Tensor, y: torch.Tensor, theta0: Optional[torch.Tensor] = None):
@@ -127,16 +145,66 @@ class DenseLinearGpu:
         if self.world > 1:
             dist.all_reduce(n, group=self.group)
         self.n_total = int(n.item())
-        self.table.write(theta0 if theta0 is not None else torch.zeros(self.d, device=self.device))
+        # collective write: the first read on any rank waits until every owner holds its slice
+        self.paracel_write("theta", theta0 if theta0 is not None else torch.zeros(self.d, device=self.device))
 
     def step(self):
-        theta = self.table.read()
-        delta = self.table.delta()
+        theta = self.paracel_read("theta")
+        delta = self.paracel_delta_buffer("theta")
         self.grad(self.X, self.y, theta, delta, self.logistic)
         if self.beta:
             # ridge / L2 shrinkage of the reference's update rule: - 2 alpha beta theta per sample
             delta.add_(theta, alpha=-2.0 * self.beta * self.y.numel())
-        self.table.bupdate(lr=-self.eta / self.n_total)
+        self.paracel_bupdate("theta", delta, "", "sgd", collective=True, lr=-self.eta / self.n_total)
+
+    # ------------------------------------------------ asynchronous methods (lr.cpp:154-299)
+    def _local_sgd(self, theta: torch.Tensor, lo: int, hi: int, alpha: float, batch: int):
+        """Minibatch SGD over rows [lo, hi) on a private copy of theta (the reference steps
+        sample by sample; a minibatch of ``batch`` rows is one gradient kernel here)."""
+        g = self._async_g
+        for b0 in range(lo, hi, batch):
+            b1 = min(hi, b0 + batch)
+            self.grad(self.X[b0:b1], self.y[b0:b1], theta, g, self.logistic)
+            theta.mul_(1.0 - 2.0 * alpha * self.beta * (b1 - b0) / batch)
+            theta.add_(g, alpha=alpha / (b1 - b0))
+        return theta
+
+    def fit_async(self, method: str = "ipm", rounds: int = 1, alpha: float = 0.05, batch: int = 4096,
+                  pull_every: int = 8, push_every: int = 10):
+        """``ipm``: every round each worker runs SGD from the shared theta over its rows and
+        the mean of the workers' moves is applied (one update per worker and round).
+        ``downpour``: SGD on a private copy; every ``push_every`` minibatches the accumulated
+        move is pushed one-sidedly (divided by the worker count) and every ``pull_every``
+        minibatches theta is read again, with no synchronisation between workers.
+        ``agd``: read and push around every minibatch."""
+        if method not in ("ipm", "downpour", "agd"):
+            raise ValueError("method must be ipm, downpour or agd")
+        n, W = self.y.numel(), self.world
+        self._async_g = torch.empty(self.d, device=self.device)
+        if method == "agd":
+            pull_every = push_every = 1
+        for _ in range(rounds):
+            theta = self.paracel_read("theta").clone()
+            base = theta.clone()
+            if method == "ipm":
+                self._local_sgd(theta, 0, n, alpha, batch)
+                self.paracel_update("theta", (theta - base) / W, "", "lr_theta_update").result()
+                self.paracel_sync()
+                continue
+            nb = 0
+            for b0 in range(0, n, batch):
+                self._local_sgd(theta, b0, min(n, b0 + batch), alpha, batch)
+                nb += 1
+                if nb % push_every == 0:
+                    self.paracel_update("theta", (theta - base) / W, "", "lr_theta_update")
+                    base.copy_(theta)
+                if nb % pull_every == 0:
+                    move = theta - base          # keep what has not been pushed yet
+                    theta = self.paracel_read("theta").clone()
+                    base = theta.clone()
+                    theta.add_(move)
+            self.paracel_update("theta", (theta - base) / W, "", "lr_theta_update").result()
+            self.paracel_sync()
 
     def mean_loss(self) -> float:
         t = self.grad.loss.clone()
@@ -145,8 +213,8 @@ class DenseLinearGpu:
         return float(t.item()) / max(self.n_total, 1)
 
     def weights(self) -> torch.Tensor:
-        return self.table.read().clone()
+        return self.paracel_read("theta").clone()
 
     def free(self):
-        torch.cuda.synchronize(self.device)
-        self.table.free()
+        self.table = None
+        self.close()

@@ -2,13 +2,18 @@
 in HBM (device path of the reference's ``matrix_factorization`` paralg class,
 alg/recommendation/matrix_factorization/mf.hpp:46-378).
 
-One training round keeps the reference's structure (mf.hpp:282-323):
+``MfSgdGpu`` is a ``paralg`` subclass on the device backend: the keys ``W_<uid>`` /
+``H_<iid>`` / ``usr_bias_<uid>`` / ``item_bias_<iid>`` are rows of tables sharded over the
+ranks' HBM, and one training round is the reference's round (mf.hpp:282-323) written with
+the same calls:
 
-    read_mf_paras   -> RowTable.pull   (peer loads; SSP staleness wait fused in)
+    read_mf_paras   -> paracel_read_multi(keys, out=, snapshot=)   peer loads; the SSP
+                                                                    staleness wait rides in the kernel
     local SGD pass  -> pcl_mf_sgd_pass (user-major chunks, vector reductions)
     update_mf_fac / update_mf_bias
-                    -> RowTable.push   (wgt * (new - old) reduced into the owner)
-    iter_commit     -> DeviceSspClock.commit
+                    -> paracel_bupdate_multi(keys, new, "", "mf_fac_updater", old=, wgt=)
+                                                                    wgt * (new - old) reduced at the owner
+    iter_commit     -> clock word stored into every peer's HBM
 
 ``wgt`` is 1 / (number of ranks that hold the row), gathered through a counter
 table exactly like the reference's ``<id>_u_cnt`` / ``<id>_i_cnt`` keys
@@ -27,8 +32,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _lib
-from ..parallel.ssp_device import DeviceSspClock
-from ..ps.tables import RowTable, ScalarTable
+from ..paralg import paralg
 from ..utils.decomp import npfact2d
 
 
@@ -96,30 +100,41 @@ def balanced_groups(counts: torch.Tensor, ngroups: int, spread_above: float = 0.
 
 
 def grid_rank(u: torch.Tensor, i: torch.Tensor, ugrp: torch.Tensor, igrp: torch.Tensor,
-              npx: int, npy: int) -> torch.Tensor:
+              npx: int, npy: int, by_id: bool = False) -> torch.Tensor:
     """Rank (grid row * npy + grid column) of every rating under the group tables of
-    :func:`balanced_groups`.  The ratings of a user (item) marked -1 are dealt round-robin over
-    the grid rows (columns) by their position in the list, so that row is shared by every rank
-    of the grid row (column) whatever the popularity of the other coordinate."""
+    :func:`balanced_groups`.  The ratings of a user (item) marked -1 are dealt over the grid
+    rows (columns), so that row is shared by every rank of the grid row (column) whatever the
+    popularity of the other coordinate: round-robin by their position in the list, or, with
+    ``by_id``, by the id of the other coordinate (the same pair then always lands on the same
+    rank, whoever computes it)."""
     gu = ugrp[u].to(torch.int64)
     gi = igrp[i].to(torch.int64)
+    if by_id:
+        gu = torch.where(gu < 0, i % npx, gu)
+        gi = torch.where(gi < 0, (u // npx) % npy, gi)
+        return gu * npy + gi
     pos = torch.arange(u.numel(), device=u.device, dtype=torch.int64)
     gu = torch.where(gu < 0, pos % npx, gu)
     gi = torch.where(gi < 0, (pos // npx) % npy, gi)   # independent of the row dealt above
     return gu * npy + gi
 
 
-class MfSgdGpu:
+class MfSgdGpu(paralg):
     def __init__(self, n_users: int, n_items: int, k: int = 128, alpha: float = 0.005,
                  beta: float = 0.02, rounds: int = 1, staleness: int = 2, ssp: bool = True,
-                 group=None, device=None, seed: int = 0, hot_mix: float = 1.0,
+                 group=None, device=None, seed: int = 0, hot_mix: float = 0.125,
                  sgd_blocks: int = 0, timeout_s: float = 5.0, hot_rows: int = 106,
-                 chunks_per_flush: int = 8, variant: int = 0, compact: bool = True):
+                 chunks_per_flush: int = 8, variant: int = 0, compact: bool = True,
+                 comm=None, hosts_dct_str=None, output: str = "", user_names=None,
+                 item_names=None, update_funcs=None, flush_scale: float = 0.0,
+                 flush_mode: str = "uniform"):
+        super().__init__(hosts_dct_str, comm, output, int(rounds), int(staleness) if ssp else 0,
+                         bool(ssp), wait_timeout_s=timeout_s, backend="gpu", device=device,
+                         group=group)
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.device = torch.device(device if device is not None else
-                                   f"cuda:{torch.cuda.current_device()}")
+        self.world = self.get_worker_size()
+        self.rank = self.get_worker_id()
+        self.update_funcs = list(update_funcs or ["cnt_updater", "mf_fac_updater", "mf_bias_updater"])
         self.n_users, self.n_items, self.k = int(n_users), int(n_items), int(k)
         self.D = _pad_rank(self.k)
         self.alpha, self.beta = float(alpha), float(beta)
@@ -127,7 +142,18 @@ class MfSgdGpu:
         self.staleness = int(staleness) if ssp else 0
         self.ssp = bool(ssp)
         self.seed = seed
+        # The concurrency weights are 1 / max(1, hot_mix * expected concurrent updates of the row).
+        # 1.0 damps a row by its full expected concurrency; 0.125 was the best of a sweep
+        # (1, 0.5, 0.25, 0.125, 0.06, 0.03) of held-out RMSE per epoch on Zipf(1.1) ratings against
+        # the sequential fp64 pass, and values below 0.06 start to oscillate.
         self.hot_mix = float(hot_mix)
+        # weight of a CTA's accumulated hot-row delta when it is mixed into the global row
+        # (<= 0: 1 / number of CTAs, the plain average of the replicas)
+        self.flush_scale = float(flush_scale)
+        # "uniform": every hot row is mixed with flush_scale; "per_row": rows with fewer ratings
+        # than the hottest take proportionally more of each CTA's delta (see load_ratings).
+        # Measured on Zipf(1.1) ratings the per-row weights converge worse, so uniform is the default.
+        self.flush_mode = flush_mode
         # variant 0: automatic (rank 128 -> sixteen-lanes-per-rating kernel, else the 32-lane one);
         # variant 1: 32-lanes-per-rating kernel, 2 CTAs per SM with 16 chunks in flight each;
         # variant 2 (D = 128): experimental 8-lanes-per-rating kernel, 1 CTA per SM, 64 chunks
@@ -144,12 +170,19 @@ class MfSgdGpu:
         self.chunks_per_flush = int(chunks_per_flush)
         self.npx, self.npy = npfact2d(self.world)
         self.px, self.py = self.rank // self.npy, self.rank % self.npy
-        # parameter-server tables (shards in HBM)
-        self.Wt = RowTable(self.n_users, self.D, torch.float32, group, self.device)
-        self.Ht = RowTable(self.n_items, self.D, torch.float32, group, self.device)
-        self.but = ScalarTable(self.n_users, group, self.device)
-        self.bit = ScalarTable(self.n_items, group, self.device)
-        self.clock = DeviceSspClock(self.staleness, self.rounds, group, self.device, timeout_s)
+        # parameter tables (shards in HBM) behind the reference's key names
+        self.user_names, self.item_names = user_names, item_names
+        self.W_tab = self.paracel_row_table(self.n_users, self.D, prefix="W_", names=user_names,
+                                            handler=self.update_funcs[1])
+        self.H_tab = self.paracel_row_table(self.n_items, self.D, prefix="H_", names=item_names,
+                                            handler=self.update_funcs[1])
+        self.ub_tab = self.paracel_scalar_table(self.n_users, prefix="usr_bias_", names=user_names,
+                                                handler=self.update_funcs[2])
+        self.ib_tab = self.paracel_scalar_table(self.n_items, prefix="item_bias_", names=item_names,
+                                                handler=self.update_funcs[2])
+        # the tables themselves (owner-side initialisation, tests)
+        self.Wt, self.Ht = self.W_tab.table, self.H_tab.table
+        self.but, self.bit = self.ub_tab.table, self.ib_tab.table
         self.mu = 0.0
         self.nnz = 0
         self.sse = torch.zeros(1, dtype=torch.float64, device=self.device)
@@ -161,9 +194,7 @@ class MfSgdGpu:
         self.overlap_push = os.environ.get("PCL_MF_OVERLAP_PUSH", "0") == "1"
         self._push_stream = None
         self._push_done = None
-        # optional per-phase device timing of round() (diagnostics; adds event records only)
-        self.phase_timing = False
-        self._phase_events = []
+        self.metrics_sync = False    # metrics lines also carry the pass's SSE (one D2H read per round)
 
     # ------------------------------------------------------------------ data
     def owner_of(self, ugrp: torch.Tensor, igrp: torch.Tensor) -> torch.Tensor:
@@ -239,6 +270,16 @@ class MfSgdGpu:
         conc_i = torch.full((ci.numel(),), float(P), device=dev)
         conc_i[: self.hot_T] = float(min(self.warps_per_block, P))  # replicas: per-CTA concurrency
         self.si = (1.0 / torch.clamp(self.hot_mix * conc_i * ci.to(torch.float32) / denom, min=1.0)).contiguous()
+        # Weight of one CTA's accumulated delta of a hot row when the replicas are mixed into the
+        # global row.  The hottest row takes the plain average over the CTAs (1 / blocks); a
+        # row with fewer ratings takes proportionally more, up to the full sum, so that every hot
+        # row moves by about the same number of averaged steps per mixing period.
+        self.hot_fs = None
+        if self.h16 and self.hot_T > 0 and self.flush_mode == "per_row":
+            nblk = min(self.sgd_blocks, max((nch + self.warps_per_block - 1) // self.warps_per_block, 1))
+            top = float(ci[0].item())
+            self.hot_fs = torch.clamp(top / ci[: self.hot_T].to(torch.float32).clamp(min=1.0) / nblk,
+                                      max=1.0).contiguous()
         nU, nI = self.lu.numel(), self.li.numel()
         # user rows are shared by the ranks of this grid row, item rows by those of this grid
         # column: every sharer starts its push at a different place of the (sorted) id list
@@ -266,6 +307,16 @@ class MfSgdGpu:
             self.ru, self.ri, self.rr = ru, ri, r
             self.h_ru = None
         self._sum_r = float(r.sum(dtype=torch.float64).item())
+        # the SGD kernel indexes the working copies with these local ids without looking at them
+        # again: range-check them once, here
+        if ru.numel():
+            _lib.validate_ids(ru, 0, nU, "MF rating stream (user index)", skip=-1)
+            _lib.validate_ids(ri, 0, nI, "MF rating stream (item index)")
+        # key batches of this rank's rows
+        self.kW = self.paracel_keys(self.W_tab, self.lu)
+        self.kH = self.paracel_keys(self.H_tab, self.li)
+        self.kub = self.paracel_keys(self.ub_tab, self.lu)
+        self.kib = self.paracel_keys(self.ib_tab, self.li)
         self._loaded = True
 
     def _build_compact(self, ru, ri, r):
@@ -330,39 +381,39 @@ class MfSgdGpu:
             dist.all_reduce(tot, group=self.group)
         self.mu = float(tot[0].item() / max(tot[1].item(), 1.0))
         self.total_nnz = int(tot[1].item())
-        # holder counts through counter tables
-        cu = ScalarTable(self.n_users, self.group, dev)
-        ci = ScalarTable(self.n_items, self.group, dev)
-        ones_u = torch.ones(self.lu.numel(), device=dev)
-        ones_i = torch.ones(self.li.numel(), device=dev)
-        cu.push(self.lu, ones_u)
-        ci.push(self.li, ones_i)
-        self._barrier()
-        cnt_u = torch.empty_like(ones_u)
-        cnt_i = torch.empty_like(ones_i)
-        cu.pull(self.lu, cnt_u)
-        ci.pull(self.li, cnt_i)
+        # holder counts through the keys <uid>_u_cnt / <iid>_i_cnt (mf.hpp:150-197)
+        cu = self.paracel_scalar_table(self.n_users, suffix="_u_cnt", handler=self.update_funcs[0])
+        ci = self.paracel_scalar_table(self.n_items, suffix="_i_cnt", handler=self.update_funcs[0])
+        ku, ki = self.paracel_keys(cu, self.lu), self.paracel_keys(ci, self.li)
+        self.paracel_bupdate_multi(ku, torch.ones(self.lu.numel(), device=dev), "", self.update_funcs[0])
+        self.paracel_bupdate_multi(ki, torch.ones(self.li.numel(), device=dev), "", self.update_funcs[0])
+        self.paracel_sync()
+        cnt_u = self.paracel_read_multi(ku, ssp_wait=False)
+        cnt_i = self.paracel_read_multi(ki, ssp_wait=False)
         self.wgt_u = (1.0 / cnt_u.clamp(min=1.0)).contiguous()
         self.wgt_i = (1.0 / cnt_i.clamp(min=1.0)).contiguous()
-        self._barrier()
-        cu.free()
-        ci.free()
-        self._have_cache = False
+        self.paracel_sync()
+        self.dev.drop(cu)
+        self.dev.drop(ci)
+        self.paracel_invalidate_cache()
 
     def _barrier(self):
-        torch.cuda.synchronize(self.device)
-        if self.world > 1:
-            dist.barrier(group=self.group)
+        self.paracel_sync()
 
     # ----------------------------------------------------------------- round
+    def read_mf_paras(self, ssp_wait: bool = True):
+        """The local rows of W, H and the biases from their owners (mf.hpp:202-215), with a
+        snapshot for the later delta push.  Under SSP the copies are reused while they are
+        younger than the staleness bound."""
+        self.paracel_read_multi(self.kW, out=self.Wl, snapshot=self.W0, ssp_wait=ssp_wait)
+        self.paracel_read_multi(self.kH, out=self.Hl, snapshot=self.H0, ssp_wait=ssp_wait)
+        self.paracel_read_multi(self.kub, out=self.bul, snapshot=self.bu0, ssp_wait=ssp_wait)
+        self.paracel_read_multi(self.kib, out=self.bil, snapshot=self.bi0, ssp_wait=ssp_wait)
+
     def pull(self, fused_wait: bool = True):
-        target = self.clock.wait_target() if (self.world > 1 and fused_wait) else 0
-        self.Wt.pull(self.lu, self.Wl, self.W0, self.clock.clocks, target,
-                     self.clock.timeout_ns, self.clock.status)
-        self.Ht.pull(self.li, self.Hl, self.H0)
-        self.but.pull(self.lu, self.bul, self.bu0)
-        self.bit.pull(self.li, self.bil, self.bi0)
-        self._have_cache = True
+        """Unconditional fresh read of the local rows (evaluation, the end of training)."""
+        self.paracel_invalidate_cache()
+        self.read_mf_paras(ssp_wait=fused_wait)
 
     def sgd_pass(self):
         s = _lib.stream_ptr()
@@ -370,14 +421,14 @@ class MfSgdGpu:
             pk = self.packed if self.compact else None
             _lib.call("pcl_mf_sgd_pass_h16", self.ru, self.ri, self.rr, self.ru.numel(), self.Wl, self.Hl,
                       self.bul, self.bil, self.su, self.si, self.mu, self.alpha, self.beta, self.hot_T,
-                      self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, pk,
+                      self.chunks_per_flush, self.flush_scale, self.sgd_blocks, self.sse, pk,
                       self.chdr if pk is not None else None, self.rtable if pk is not None else None,
-                      self.h16_threads, s)
+                      self.h16_threads, self.hot_fs, s)
         elif self.h_ru is None:
             pk = self.packed if (self.compact and not self.g8) else None
             _lib.call("pcl_mf_sgd_pass", self.ru, self.ri, self.rr, self.ru.numel(), self.Wl,
                       self.Hl, self.bul, self.bil, self.su, self.si, self.D, self.mu,
-                      self.alpha, self.beta, self.hot_T, self.chunks_per_flush, 0.0,
+                      self.alpha, self.beta, self.hot_T, self.chunks_per_flush, self.flush_scale,
                       self.sgd_blocks, self.sse, self.variant, pk, self.chdr if pk is not None else None,
                       self.rtable if pk is not None else None, s)
         else:
@@ -432,50 +483,47 @@ class MfSgdGpu:
             if self.h16:
                 _lib.call("pcl_mf_sgd_pass_h16", seg_args[0], seg_args[1], seg_args[2], m, self.Wl, self.Hl,
                           self.bul, self.bil, self.su, self.si, self.mu, self.alpha, self.beta, self.hot_T,
-                          self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, seg_args[3], seg_args[4],
-                          seg_args[5], self.h16_threads, main.cuda_stream)
+                          self.chunks_per_flush, self.flush_scale, self.sgd_blocks, self.sse, seg_args[3], seg_args[4],
+                          seg_args[5], self.h16_threads, self.hot_fs, main.cuda_stream)
             else:
                 _lib.call("pcl_mf_sgd_pass", seg_args[0], seg_args[1], seg_args[2], m, self.Wl, self.Hl,
                           self.bul, self.bil, self.su, self.si, self.D, self.mu, self.alpha, self.beta,
-                          self.hot_T, self.chunks_per_flush, 0.0, self.sgd_blocks, self.sse, self.variant,
+                          self.hot_T, self.chunks_per_flush, self.flush_scale, self.sgd_blocks, self.sse, self.variant,
                           seg_args[3], seg_args[4], seg_args[5], main.cuda_stream)
             self._consumed[b].record(main)
             k += 1
 
+    def update_mf(self, start_u: int = 0, start_i: int = 0):
+        """Push ``wgt * (new - old)`` of every local row to its owner (update_mf_fac /
+        update_mf_bias, mf.hpp:217-262) and refresh the snapshots."""
+        fac, bias = self.update_funcs[1], self.update_funcs[2]
+        with self.phase("push_W"):
+            self.paracel_bupdate_multi(self.kW, self.Wl, "", fac, old=self.W0, wgt=self.wgt_u, start=start_u)
+        with self.phase("push_H"):
+            self.paracel_bupdate_multi(self.kH, self.Hl, "", fac, old=self.H0, wgt=self.wgt_i, start=start_i)
+        with self.phase("push_bias"):
+            self.paracel_bupdate_multi(self.kub, self.bul, "", bias, old=self.bu0, wgt=self.wgt_u)
+            self.paracel_bupdate_multi(self.kib, self.bil, "", bias, old=self.bi0, wgt=self.wgt_i)
+
     def push(self):
-        self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u)
-        self.Ht.push(self.li, self.Hl, self.H0, self.wgt_i)
-        self.but.push(self.lu, self.bul, self.bu0, self.wgt_u)
-        self.bit.push(self.li, self.bil, self.bi0, self.wgt_i)
+        self.update_mf()
 
-    def need_pull(self) -> bool:
-        """SSP cache rule (include/ps.hpp:437-457): first and last read always pull; with
-        staleness s a cached copy may be reused while it is less than s clocks old."""
-        c = self.clock.clock
-        if not self._have_cache or not self.ssp or self.staleness == 0:
-            return True
-        if c == 0 or c >= self.rounds:
-            return True
-        return (c - self._pulled_at) >= self.staleness
+    @property
+    def phase_timing(self) -> bool:
+        return self.timer is not None
 
-    def _mark(self, label: str):
-        if self.phase_timing:
-            e = torch.cuda.Event(enable_timing=True)
-            e.record()
-            self._phase_events.append((label, e))
+    @phase_timing.setter
+    def phase_timing(self, on: bool):
+        """Per-phase device timing of round() (diagnostics; adds event records only)."""
+        from ..utils.metrics import PhaseTimer
+        self.timer = PhaseTimer() if on else None
 
     def _push_sync(self):
-        self.Wt.push(self.lu, self.Wl, self.W0, self.wgt_u, start=self._start_u)
-        self._mark("push_W")
-        self.Ht.push(self.li, self.Hl, self.H0, self.wgt_i, start=self._start_i)
-        self._mark("push_H")
-        self.but.push(self.lu, self.bul, self.bu0, self.wgt_u)
-        self.bit.push(self.li, self.bil, self.bi0, self.wgt_i)
-        self._mark("push_bias")
-        if not self.ssp and self.world > 1:
-            self._barrier()
-        self.clock.commit()
-        self._mark("commit")
+        self.update_mf(self._start_u, self._start_i)
+        with self.phase("commit"):
+            if not self.ssp and self.world > 1:
+                self.paracel_sync()
+            self.iter_commit()
 
     def _push_overlapped(self):
         """Push + commit on a side stream while the main stream goes on with the next round.
@@ -494,68 +542,79 @@ class MfSgdGpu:
             self._Hs = torch.empty_like(self.Hl)
             self._bus = torch.empty_like(self.bul)
             self._bis = torch.empty_like(self.bil)
-        if self._push_done is not None:
-            main.wait_event(self._push_done)      # staging buffers are free again
-        self._Ws.copy_(self.Wl)
-        self._Hs.copy_(self.Hl)
-        self._bus.copy_(self.bul)
-        self._bis.copy_(self.bil)
+        with self.phase("stage"):
+            if self._push_done is not None:
+                main.wait_event(self._push_done)      # staging buffers are free again
+            self._Ws.copy_(self.Wl)
+            self._Hs.copy_(self.Hl)
+            self._bus.copy_(self.bul)
+            self._bis.copy_(self.bil)
         staged = torch.cuda.Event()
         staged.record(main)
-        self._mark("stage")
+        fac, bias = self.update_funcs[1], self.update_funcs[2]
         with torch.cuda.stream(self._push_stream):
             self._push_stream.wait_event(staged)
-            self.Wt.push(self.lu, self._Ws, self.W0, self.wgt_u, start=self._start_u)
-            self.Ht.push(self.li, self._Hs, self.H0, self.wgt_i, start=self._start_i)
-            self.but.push(self.lu, self._bus, self.bu0, self.wgt_u)
-            self.bit.push(self.li, self._bis, self.bi0, self.wgt_i)
-            self.clock.commit()
+            self.paracel_bupdate_multi(self.kW, self._Ws, "", fac, old=self.W0, wgt=self.wgt_u,
+                                       start=self._start_u)
+            self.paracel_bupdate_multi(self.kH, self._Hs, "", fac, old=self.H0, wgt=self.wgt_i,
+                                       start=self._start_i)
+            self.paracel_bupdate_multi(self.kub, self._bus, "", bias, old=self.bu0, wgt=self.wgt_u)
+            self.paracel_bupdate_multi(self.kib, self._bis, "", bias, old=self.bi0, wgt=self.wgt_i)
+            self.iter_commit()
             self._push_done = torch.cuda.Event()
             self._push_done.record(self._push_stream)
 
     def round(self):
-        self._mark("start")
-        if self.need_pull():
-            if self._push_done is not None:       # the pull must see this rank's own pushes
+        with self.phase("pull_or_wait"):
+            if self._push_done is not None and self.paracel_would_pull(self.kW, self.Wl):
+                # the pull must see this rank's own pushes
                 torch.cuda.current_stream(self.device).wait_event(self._push_done)
-            self.pull()
-            self._pulled_at = self.clock.clock
-        elif self.world > 1:
-            self.clock.wait()  # keep the staleness bound while serving from the cache
-        self._mark("pull_or_wait")
-        self.sse.zero_()
-        self.sgd_pass()
-        self._mark("sgd")
+            self.read_mf_paras()
+        with self.phase("sgd"):
+            self.sse.zero_()
+            self.sgd_pass()
         if self.overlap_push and self.world > 1 and self.ssp and self.staleness >= 2:
             self._push_overlapped()
         else:
             self._push_sync()
+        if self.metrics is not None:
+            rows = self.lu.numel() + self.li.numel()
+            self.log_metrics(round=self.clock, ratings=self.nnz, rows_held=rows,
+                             bytes_pulled=rows * (self.D + 1) * 4, bytes_pushed=rows * (self.D + 1) * 4,
+                             h2d_bytes=self.h2d_bytes, staleness=self.staleness,
+                             sse_of_pass=float(self.sse.item()) if self.metrics_sync else None)
 
     def phase_times_ms(self):
         """Mean device time of each phase of round() over the rounds run since ``phase_timing``
         was switched on (synchronises)."""
-        torch.cuda.synchronize(self.device)
-        out: Dict[str, float] = {}
-        rounds = 0
-        prev = None
-        for label, e in self._phase_events:
-            if label == "start":
-                rounds += 1
-            else:
-                out[label] = out.get(label, 0.0) + prev.elapsed_time(e)
-            prev = e
-        out = {k: v / max(rounds, 1) for k, v in out.items()}
+        summ = self.phase_summary()
+        rounds = int(summ.get("sgd", {}).get("count", 0))
+        out: Dict[str, float] = {k: v["ms"] / max(rounds, 1) for k, v in summ.items()}
         out["rounds"] = rounds
-        self._phase_events = []
         return out
 
+    def checkpoint_extra(self):
+        return {"mu": self.mu, "total_nnz": self.total_nnz}
+
+    def restore_extra(self, extra):
+        self.mu, self.total_nnz = float(extra["mu"]), int(extra["total_nnz"])
+
     def fit(self):
-        for _ in range(self.rounds):
+        """Run the rounds that are left (all of them, or the rest after ``load_checkpoint``)."""
+        for _ in range(self.clock, self.rounds):
             self.round()
-        self._barrier()
-        self.clock.check()
+        self.paracel_sync()
+        self.paracel_check()
         self.pull(fused_wait=False)
-        self._barrier()
+        self.paracel_sync()
+
+    def solve(self):
+        """``init_parameters`` + ``learning`` of the reference's solve() (mf.hpp:325-335); the
+        ratings must have been loaded with ``load_ratings``."""
+        self.init_parameters()
+        self.set_total_iters(self.rounds)
+        self.paracel_sync()
+        self.fit()
 
     # --------------------------------------------------------------- metrics
     def running_rmse(self) -> float:
@@ -601,45 +660,54 @@ class MfSgdGpu:
                   self.D, self.mu, None, pred, _lib.stream_ptr())
         return pred
 
+    def heldout_sse(self, u: torch.Tensor, i: torch.Tensor, r: torch.Tensor, chunk: int = 1 << 18):
+        """Sum of squared errors of the clipped estimate on (user, item, rating) triples this
+        rank has not trained on.  The rows come from their owners' shards through
+        ``paracel_read_multi`` (any id, not only the rows this rank holds).  Returns
+        ``(sse, count)`` as Python floats; all-reduce them for the global RMSE."""
+        dev = self.device
+        u, i = u.to(dev, torch.int64), i.to(dev, torch.int64)
+        r = r.to(dev, torch.float32)
+        sse = torch.zeros((), dtype=torch.float64, device=dev)
+        for s0 in range(0, u.numel(), chunk):
+            uu, ii = u[s0:s0 + chunk].contiguous(), i[s0:s0 + chunk].contiguous()
+            W = self.paracel_read_multi(self.paracel_keys(self.W_tab, uu), ssp_wait=False, use_cache=False)
+            H = self.paracel_read_multi(self.paracel_keys(self.H_tab, ii), ssp_wait=False, use_cache=False)
+            bu = self.paracel_read_multi(self.paracel_keys(self.ub_tab, uu), ssp_wait=False, use_cache=False)
+            bi = self.paracel_read_multi(self.paracel_keys(self.ib_tab, ii), ssp_wait=False, use_cache=False)
+            pred = (self.mu + bu + bi + (W * H).sum(1)).clamp_(1.0, 5.0)
+            sse += ((pred - r[s0:s0 + chunk]).double() ** 2).sum()
+        return float(sse.item()), float(u.numel())
+
     # ------------------------------------------------------------------ dump
-    def dump_result(self, outdir: str, user_names=None, item_names=None):
+    def dump_result(self, outdir: str = "", user_names=None, item_names=None):
         """Write miu_0, ubias_0, ibias_0, W_0, H_0 in the reference's text layout
-        (mf.hpp:380-492): rank 0 writes what each owner holds, shard by shard.  ``user_names`` /
-        ``item_names`` (arrays indexed by the dense id) give the ids to print."""
+        (mf.hpp:380-492).  As there, worker 0 reads each kind of key with its filter
+        (``paracel_read_special``; the rows come out of the owners' HBM over NVLink) and writes
+        them.  The ids printed are those of the key names; ``user_names`` / ``item_names``
+        (arrays indexed by row) rename them when the tables were built without names."""
         from ..utils.dump import dump_dict_scalar, dump_dict_vector
-        os.makedirs(outdir, exist_ok=True)
-        self._barrier()
-        parts = {}
-        for name, t, width in (("W_", self.Wt, self.k), ("H_", self.Ht, self.k)):
-            ids = t.owned_ids().cpu()
-            vals = t.shard[: ids.numel(), :width].cpu()
-            parts[name] = (ids, vals)
-        for name, t in (("ubias_", self.but), ("ibias_", self.bit)):
-            ids = t.owned_ids().cpu()
-            parts[name] = (ids, t.shard[: ids.numel()].cpu())
-        gathered = [parts]
-        if self.world > 1:
-            gathered = [None] * self.world
-            dist.all_gather_object(gathered, parts, group=self.group)
+        outdir = outdir or self.output
+        self.paracel_sync()
         if self.rank == 0:
+            os.makedirs(outdir, exist_ok=True)
             dump_dict_scalar({"miu": self.mu, "rating_sz": float(self.total_nnz)},
                              os.path.join(outdir, "miu_0"))
-            def keys(name, ids):
-                tab = user_names if name in ("ubias_", "W_") else item_names
-                return ids.tolist() if tab is None else [int(tab[j]) for j in ids.tolist()]
-            for name in ("ubias_", "ibias_"):
-                with open(os.path.join(outdir, name + "0"), "w") as f:
-                    for p in gathered:
-                        ids, vals = p[name]
-                        dump_dict_scalar(dict(zip(keys(name, ids), vals.tolist())), f)
-            for name in ("W_", "H_"):
-                with open(os.path.join(outdir, name + "0"), "w") as f:
-                    for p in gathered:
-                        ids, vals = p[name]
-                        dump_dict_vector(dict(zip(keys(name, ids), vals.tolist())), f)
-        self._barrier()
+
+            def ident(key, user):
+                j = int(key.rsplit("_", 1)[1])
+                tab = user_names if user else item_names
+                own = self.user_names if user else self.item_names
+                return j if (tab is None or own is not None) else int(tab[j])
+            for fname, flt, user in (("ubias_0", "mf_ubias_filter", True), ("ibias_0", "mf_ibias_filter", False)):
+                d = self.paracel_read_special("", flt)
+                dump_dict_scalar({ident(k_, user): v for k_, v in d.items()}, os.path.join(outdir, fname))
+            for fname, flt, user in (("W_0", "mf_W_filter", True), ("H_0", "mf_H_filter", False)):
+                d = self.paracel_read_special("", flt)
+                dump_dict_vector({ident(k_, user): v[: self.k] for k_, v in d.items()},
+                                 os.path.join(outdir, fname))
+        self.paracel_sync()
 
     def free(self):
-        self._barrier()
-        for t in (self.Wt, self.Ht, self.but, self.bit, self.clock):
-            t.free()
+        self.Wt = self.Ht = self.but = self.bit = None
+        self.close()

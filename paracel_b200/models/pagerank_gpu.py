@@ -3,12 +3,15 @@ alg/graph_alg/pagerank/pr.hpp:40-200).
 
 Vertices are dense ids in [0, n); rank r owns the range ``[r*S, (r+1)*S)`` and keeps the
 in-links of its vertices as CSR.  What travels between ranks is the contribution vector
-``c(u) = pr(u) / outdeg(u)``: an iteration is ``read`` (all-gather of all shards by peer
-loads) and one pull kernel that evaluates ``pr(v) = (1 - d) + d * sum_{u->v} c(u)`` and writes
-the new contribution of every owned vertex straight into the owner's shard of the OTHER of
-two ping-pong tables (the reference's read_multi + write_multi, pr.hpp:140-168, without
-string keys).  Out-degrees are reduced through a ``DenseTable`` with the add handler.  An edge
-whose target is the sentinel 2147483648 only marks its source as a vertex with out-links."""
+``c(u) = pr(u) / outdeg(u)``.  ``PageRankGpu`` is a ``paralg`` subclass on the device backend
+with two dense keys, ``pr_contrib_0`` and ``pr_contrib_1``; an iteration is
+``paracel_read`` of the current key (all-gather of all shards by peer loads) and one pull
+kernel that evaluates ``pr(v) = (1 - d) + d * sum_{u->v} c(u)`` and writes the new
+contribution of every owned vertex straight into this rank's shard of the OTHER key
+(``paracel_local_shard`` + ``paracel_commit_write``: the reference's read_multi +
+write_multi, pr.hpp:140-168).  Out-degrees are reduced with a collective ``paracel_bupdate``
+(add handler).  An edge whose target is the sentinel 2147483648 only marks its source as a
+vertex with out-links."""
 from __future__ import annotations
 
 import os
@@ -17,20 +20,23 @@ from typing import Dict, Optional
 import torch
 import torch.distributed as dist
 
+from ..ops import _lib
 from ..ops.linear import pagerank_pull, pagerank_pull_stream, pagerank_stream_plan
-from ..ps.tables import DenseTable
+from ..paralg import paralg
 from ..utils.types import SENTINEL
 
 
-class PageRankGpu:
+class PageRankGpu(paralg):
+    KEYS = ("pr_contrib_0", "pr_contrib_1")
+
     def __init__(self, n_vertices: int, damping: float = 0.85, group=None, device=None,
-                 threads_per_row: int = 8, edge_balanced: bool = True):
+                 threads_per_row: int = 8, edge_balanced: bool = True, comm=None,
+                 hosts_dct_str=None, output: str = ""):
+        super().__init__(hosts_dct_str, comm, output, backend="gpu", device=device, group=group)
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world, self.rank = self.get_worker_size(), self.get_worker_id()
         self.n, self.d = int(n_vertices), float(damping)
-        self.tables = [DenseTable(self.n, group, device, handler="add") for _ in range(2)]
-        self.device = self.tables[0].device
+        self.tables = [self.paracel_dense_table(k, self.n, handler="add").table for k in self.KEYS]
         self.S = self.tables[0].S
         self.lo, self.hi = self.tables[0].owned_range()
         self.n_local = max(0, self.hi - self.lo)
@@ -48,13 +54,14 @@ class PageRankGpu:
         dev = self.device
         src = src.to(dev, torch.int64)
         dst = dst.to(dev, torch.int64)
-        t = self.tables[0]
+        k0 = self.KEYS[0]
+        _lib.validate_ids(src, 0, self.n, "PageRank edges (source ids)")
+        _lib.validate_ids(dst, 0, self.n, "PageRank edges (target ids)", skip=SENTINEL)
         # out-degrees: reduce-scatter(add) of the local source counts
-        t.write(torch.zeros(self.n, device=dev))
-        t.delta().copy_(torch.bincount(src, minlength=self.n).to(torch.float32))
-        t.bupdate(handler="add")
-        outdeg_full = t.read().clone()
-        torch.cuda.synchronize(dev)
+        self.paracel_write(k0, torch.zeros(self.n, device=dev))
+        self.paracel_delta_buffer(k0).copy_(torch.bincount(src, minlength=self.n).to(torch.float32))
+        self.paracel_bupdate(k0, self.paracel_delta_buffer(k0), "", "add", collective=True)
+        outdeg_full = self.paracel_read(k0).clone()
         self._barrier()
         real = dst != SENTINEL
         src, dst = src[real], dst[real]
@@ -78,20 +85,20 @@ class PageRankGpu:
         self.acc = torch.zeros(max(self.n_local, 1), device=dev)
         self.plan = pagerank_stream_plan(self.row_ptr)
         # contribution table for iteration 0 lives in tables[0]
-        for tb in self.tables:
-            tb.shard.zero_()
-        self.tables[0].shard[: self.n_local] = self.rank_local * self.inv_outdeg
-        self.tables[0].mark_written()
+        for k in self.KEYS:
+            self.paracel_local_shard(k).zero_()
+        self.paracel_local_shard(k0)[: self.n_local] = self.rank_local * self.inv_outdeg
+        self.paracel_commit_write(k0)
         self.it = 0
 
     def _barrier(self):
-        torch.cuda.synchronize(self.device)
-        if self.world > 1:
-            dist.barrier(group=self.group)
+        self.paracel_sync()
 
     def step(self, track_delta: bool = False):
+        kcur, knxt = self.KEYS[self.it % 2], self.KEYS[(self.it + 1) % 2]
         cur, nxt = self.tables[self.it % 2], self.tables[(self.it + 1) % 2]
-        contrib = cur.read(copy=False)   # the pull kernel writes the OTHER table
+        # the pull kernel writes the OTHER key, so a single rank may read its shard in place
+        contrib = cur.read(copy=False) if self.world == 1 else self.paracel_read(kcur)
         if track_delta:
             self.delta_l1.zero_()
         if self.edge_balanced:
@@ -103,16 +110,24 @@ class PageRankGpu:
                           nxt.shard, self.rank_new, self.delta_l1 if track_delta else None,
                           self.rank_local if track_delta else None, self.tpr,
                           self.heavy_rows if self.heavy_rows.numel() else None, self.heavy_deg)
-        nxt.mark_written()
+        self.paracel_commit_write(knxt)
         self.rank_local, self.rank_new = self.rank_new, self.rank_local
         self.it += 1
 
+    def checkpoint_extra(self):
+        return {"rank_local": self.rank_local, "it": self.it}
+
+    def restore_extra(self, extra):
+        self.rank_local.copy_(extra["rank_local"].to(self.device))
+        self.it = int(extra["it"])
+
     def run(self, rounds: int):
         for _ in range(rounds):
-            self.step()
+            with self.phase("iteration"):
+                self.step()
+            self.log_metrics(iteration=self.it, edges=self.n_edges_local)
         self._barrier()
-        for t in self.tables:
-            t.check()
+        self.paracel_check()
 
     def ranks(self) -> torch.Tensor:
         """Ranks of the owned vertices (vertices without out-links are reported as well)."""
@@ -140,6 +155,5 @@ class PageRankGpu:
         self._barrier()
 
     def free(self):
-        self._barrier()
-        for t in self.tables:
-            t.free()
+        self.tables = []
+        self.close()

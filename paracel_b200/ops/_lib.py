@@ -36,14 +36,14 @@ SIGS = {
     "pcl_symm_close": "p",
     "pcl_symm_free": "p",
     "pcl_device_sync": "",
-    "pcl_rows_pull_f32": "ppiiqpppqQpip",
-    "pcl_rows_push_f32": "ppiiqpppfiiqp",
-    "pcl_scalars_pull_f32": "ppiqppp",
-    "pcl_scalars_push_f32": "ppiqpppip",
-    "pcl_rows_pull_i32": "ppiiqppp",
-    "pcl_rows_push_i32": "ppiiqppip",
+    "pcl_rows_pull_f32": "ppiiqpppqQpiqp",
+    "pcl_rows_push_f32": "ppiiqpppfiiqqpip",
+    "pcl_scalars_pull_f32": "ppiqppqpip",
+    "pcl_scalars_push_f32": "ppiqpppiiqpip",
+    "pcl_rows_pull_i32": "ppiiqppqpip",
+    "pcl_rows_push_i32": "ppiiqppiqpip",
     "pcl_mf_sgd_pass": "pppqppppppifffiifipipppp",
-    "pcl_mf_sgd_pass_h16": "pppqppppppfffiifippppip",
+    "pcl_mf_sgd_pass_h16": "pppqppppppfffiifippppipp",
     "pcl_mf_sse": "pppqppppifppp",
     "pcl_gemm_tf32": "pppiiiqipppppiiiiipip",
     "pcl_gemm_tf32_2sm": "pppiiiqipppppiiiiipip",
@@ -51,6 +51,8 @@ SIGS = {
     "pcl_dense_read": "ppqqiipqQpp",
     "pcl_dense_bupdate": "ppqqiiiffpqQppppp",
     "pcl_publish_flag": "piiqp",
+    "pcl_dense_push": "ppqqiifp",
+    "pcl_validate_ids": "piqqqqpip",
     "pcl_lr_dense_grad": "pppqiippppip",
     "pcl_lr_sparse_grad": "pppppqiippip",
     "pcl_pagerank_pull": "ppppqfppppiqpip",
@@ -64,8 +66,11 @@ SIGS = {
     "pcl_partition_count": "ppqiipp",
     "pcl_partition_scatter": "pppqiipqppppip",
     "pcl_gram": "pqipp",
+    "pcl_spmm_csr": "pppqpipp",
+    "pcl_spmm_csr_t": "pppqpipp",
+    "pcl_chol_factor": "pippdpp",
     "pcl_allreduce_sum_f64": "ppipppiiiqQpp",
-    "pcl_ssp_commit": "piiqp",
+    "pcl_ssp_commit": "piiqpp",
     "pcl_ssp_wait": "piqQpip",
 }
 
@@ -148,6 +153,60 @@ def call(name: str, *args) -> None:
     if rc != 0:
         msg = lib.pcl_error_string(rc).decode()
         raise RuntimeError(f"{name} failed: CUDA error {rc} ({msg})")
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded device-side wait (SSP clock, table flag, tile flag) ran out."""
+
+    def __init__(self, what, rank, wait_id, expected, seen):
+        super().__init__(f"{what}: rank {rank}: device wait {wait_id} timed out: expected >= "
+                         f"{expected}, saw {seen}")
+        self.rank, self.wait_id, self.expected, self.seen = rank, wait_id, expected, seen
+
+
+class BadDeviceId(IndexError):
+    """A kernel met an id outside its table; the access was skipped."""
+
+    def __init__(self, what, rank, where, position, bad_id):
+        super().__init__(f"{what}: rank {rank}: id {bad_id} at position {position} is outside the "
+                         f"table (kernel {where}); the access was skipped")
+        self.rank, self.where, self.position, self.bad_id = rank, where, position, bad_id
+
+
+def new_status(device) -> torch.Tensor:
+    """A zeroed status block (``PclStatus``: code, rank, wait id, pad as four 32-bit words, then
+    the expected and the seen value as 64-bit words) that kernels report through."""
+    return torch.zeros(4, dtype=torch.int64, device=device)
+
+
+def check_status(status: torch.Tensor, what: str = "device status") -> None:
+    """Read a status block back (synchronises its stream), clear it and raise what it holds:
+    code 1 -> :class:`DeviceWaitTimeout`, code 2 -> :class:`BadDeviceId`."""
+    st = status.cpu()
+    word0 = int(st[0].item())
+    code = word0 & 0xFFFFFFFF
+    if code == 0:
+        return
+    rank = (word0 >> 32) & 0xFFFFFFFF
+    where = int(st[1].item()) & 0xFFFFFFFF
+    a, b = int(st[2].item()), int(st[3].item())
+    status.zero_()
+    if code == 2:
+        raise BadDeviceId(what, rank, where, a, b)
+    raise DeviceWaitTimeout(what, rank, where, a, b)
+
+
+def validate_ids(ids: torch.Tensor, lo: int, hi: int, what: str, skip=None) -> None:
+    """Range check of an id array on the device (one pass, then one 32-byte read): raises
+    :class:`BadDeviceId` if an element is outside ``[lo, hi)`` and not equal to ``skip``."""
+    if ids.numel() == 0:
+        return
+    if ids.dtype not in (torch.int32, torch.int64) or not ids.is_contiguous():
+        raise ValueError(f"{what}: ids must be contiguous int32 or int64")
+    st = new_status(ids.device)
+    call("pcl_validate_ids", ids, int(ids.dtype == torch.int64), ids.numel(), int(lo), int(hi),
+         int(lo if skip is None else skip), st, 0, stream_ptr())
+    check_status(st, what)
 
 
 def check_cuda(t: torch.Tensor, dtype, name: str):

@@ -48,7 +48,16 @@ class DeviceSspClock:
     def commit(self):
         self.clock += 1
         value = DEPARTED if self.clock >= self.total_iters else self.clock
-        _lib.call("pcl_ssp_commit", self.buf.ptr_table, self.world, self.rank, value,
+        _lib.call("pcl_ssp_commit", self.buf.ptr_table, self.world, self.rank, value, self.status,
+                  _lib.stream_ptr())
+
+    def restore(self, clock: int):
+        """Resume at ``clock`` (collective, after a checkpoint load): set the local counter and
+        store the value into every peer's clock array, as the commit that ended iteration
+        ``clock - 1`` did."""
+        self.clock = int(clock)
+        value = DEPARTED if self.clock >= self.total_iters else self.clock
+        _lib.call("pcl_ssp_commit", self.buf.ptr_table, self.world, self.rank, value, self.status,
                   _lib.stream_ptr())
 
     def wait(self):

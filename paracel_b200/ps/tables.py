@@ -11,6 +11,13 @@ registered for the table (add, scaled add, max) runs at the owner as part of
 the reduction.
 
 ``ScalarTable`` is the width-1 case (biases, counters).
+
+Every kernel that takes ids checks them against the table's extent; an id
+outside ``[0, rows)`` is skipped and reported through the table's status block,
+which ``check()`` turns into :class:`~paracel_b200.ops._lib.BadDeviceId`.  A
+push whose status block already holds an error (a staleness wait of the same
+round that ran out) does nothing, so a rank that could not pull does not mix
+stale copies into the shared tables.
 """
 from __future__ import annotations
 
@@ -21,7 +28,7 @@ import torch
 from ..ops import _lib
 from ..parallel.symm import SymmBuffer
 
-HANDLERS = {"add": 0, "scaled_add": 1, "max": 2}
+HANDLERS = {"add": 0, "scaled_add": 1, "max": 2, "assign": 3}
 
 
 class RowTable:
@@ -36,6 +43,11 @@ class RowTable:
         self.buf = SymmBuffer(self.rows_per_shard * self.width, dtype, group, device)
         self.shard = self.buf.local.view(self.rows_per_shard, self.width)
         self.device = self.buf.device
+        self.status = _lib.new_status(self.device)
+
+    def check(self, what: str = "row table"):
+        """Synchronise and raise if a kernel on this table reported a bad id or a timed-out wait."""
+        _lib.check_status(self.status, what)
 
     # global ids owned by this rank, in local-row order
     def owned_ids(self) -> torch.Tensor:
@@ -46,37 +58,45 @@ class RowTable:
     def pull(self, ids: torch.Tensor, out: torch.Tensor, snapshot: Optional[torch.Tensor] = None,
              clocks: Optional[torch.Tensor] = None, target: int = 0,
              timeout_ns: int = 2_000_000_000, status: Optional[torch.Tensor] = None):
+        """``status``: block that the fused staleness wait and the id check report through
+        (default: the table's own)."""
         _lib.check_cuda(ids, torch.int64, "ids")
         _lib.check_cuda(out, self.dtype, "out")
         n = ids.numel()
         assert out.numel() == n * self.width
         s = _lib.stream_ptr()
+        st = self.status if status is None else status
         if self.dtype == torch.float32:
             _lib.call("pcl_rows_pull_f32", ids, self.buf.ptr_table, self.world, self.width, n,
-                      out, snapshot, clocks, int(target), int(timeout_ns), status, self.rank, s)
+                      out, snapshot, clocks, int(target), int(timeout_ns), st, self.rank,
+                      self.rows, s)
         elif self.dtype == torch.int32:
             _lib.call("pcl_rows_pull_i32", ids, self.buf.ptr_table, self.world, self.width, n,
-                      out, snapshot, s)
+                      out, snapshot, self.rows, st, self.rank, s)
         else:
             raise TypeError(self.dtype)
 
     def push(self, ids: torch.Tensor, cur: torch.Tensor, old: Optional[torch.Tensor] = None,
              wgt: Optional[torch.Tensor] = None, handler: str = "add", scale: float = 1.0,
-             refresh_old: bool = True, start: int = 0):
+             refresh_old: bool = True, start: int = 0, status: Optional[torch.Tensor] = None):
         """``start``: first row of ``ids`` to visit (the kernel wraps around).  Ranks that push the
-        same rows at the same time should pass different values."""
+        same rows at the same time should pass different values.  Handler ``max`` needs values
+        that are not NaN; ``assign`` stores ``cur`` (``paracel_write_multi``)."""
         _lib.check_cuda(ids, torch.int64, "ids")
         _lib.check_cuda(cur, self.dtype, "cur")
         n = ids.numel()
+        assert cur.numel() == n * self.width
         s = _lib.stream_ptr()
+        st = self.status if status is None else status
         if self.dtype == torch.float32:
             _lib.call("pcl_rows_push_f32", ids, self.buf.ptr_table, self.world, self.width, n,
-                      cur, old, wgt, float(scale), HANDLERS[handler], int(refresh_old), int(start), s)
+                      cur, old, wgt, float(scale), HANDLERS[handler], int(refresh_old), int(start),
+                      self.rows, st, self.rank, s)
         else:
             if handler != "add" or wgt is not None:
                 raise ValueError("int32 tables support the add handler only")
             _lib.call("pcl_rows_push_i32", ids, self.buf.ptr_table, self.world, self.width, n,
-                      cur, old, int(refresh_old), s)
+                      cur, old, int(refresh_old), self.rows, st, self.rank, s)
 
     def free(self):
         self.shard = None
@@ -93,29 +113,47 @@ class ScalarTable:
         self.buf = SymmBuffer(self.rows_per_shard, torch.float32, group, device)
         self.shard = self.buf.local
         self.device = self.buf.device
+        self.width, self.dtype = 1, torch.float32
+        self.status = _lib.new_status(self.device)
+
+    def check(self, what: str = "scalar table"):
+        _lib.check_status(self.status, what)
 
     def owned_ids(self) -> torch.Tensor:
         ids = torch.arange(self.rows_per_shard, device=self.device, dtype=torch.int64)
         ids = ids * self.world + self.rank
         return ids[ids < self.rows]
 
-    def pull(self, ids, out, snapshot=None):
+    def pull(self, ids, out, snapshot=None, status=None):
+        _lib.check_cuda(ids, torch.int64, "ids")
         _lib.call("pcl_scalars_pull_f32", ids, self.buf.ptr_table, self.world, ids.numel(),
-                  out, snapshot, _lib.stream_ptr())
+                  out, snapshot, self.rows, self.status if status is None else status, self.rank,
+                  _lib.stream_ptr())
 
-    def push(self, ids, cur, old=None, wgt=None, refresh_old=True):
+    def push(self, ids, cur, old=None, wgt=None, refresh_old=True, handler: str = "add",
+             status=None, **_ignored):
+        _lib.check_cuda(ids, torch.int64, "ids")
         _lib.call("pcl_scalars_push_f32", ids, self.buf.ptr_table, self.world, ids.numel(),
-                  cur, old, wgt, int(refresh_old), _lib.stream_ptr())
+                  cur, old, wgt, int(refresh_old), HANDLERS[handler], self.rows,
+                  self.status if status is None else status, self.rank, _lib.stream_ptr())
 
     def free(self):
         self.shard = None
         self.buf.free()
 
 
-DENSE_HANDLERS = {"add": 0, "sgd": 1, "prox_l1": 2, "max": 3,
-                  # handler names of the reference that are plain adds
-                  "lr_theta_update": 0, "ridge_theta_update": 0, "default_incr_ld": 0,
-                  "default_incr_lf": 0, "svd_updater": 0, "local_update_kmeans_clusters": 0}
+DENSE_KINDS = {"add": 0, "sgd": 1, "prox_l1": 2, "max": 3}
+
+
+def _dense_kind(name: str):
+    """(kernel code, registered lr, registered lambda) of a handler name on a dense table."""
+    from .device_handlers import resolve_device_handler
+    h = resolve_device_handler(name)
+    if h.kind == "scaled_add":          # theta += scale * sum  ==  sgd with lr = -scale
+        return DENSE_KINDS["sgd"], -(h.scale if h.scale is not None else 1.0), h.lam
+    if h.kind not in DENSE_KINDS:
+        raise ValueError(f"handler {name!r} ({h.kind}) cannot run as a dense bupdate")
+    return DENSE_KINDS[h.kind], h.lr, h.lam
 
 
 class DenseTable:
@@ -152,6 +190,7 @@ class DenseTable:
         self.status = torch.zeros(4, dtype=torch.int64, device=self.device)
         self.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.nnz = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self.count_nnz = False     # bupdate also counts the non-zeros of the new shard into nnz
         base = self.delta_buf.ptr_table
         self._delta_tables = [base.clone(), (base + self.Lp * 4).contiguous()]
         self._ready_table = self.flag_buf.ptr_table.clone()
@@ -178,17 +217,22 @@ class DenseTable:
         return self.full[: self.L]
 
     def bupdate(self, handler: Optional[str] = None, lr: Optional[float] = None,
-                lam: Optional[float] = None, count_nnz: bool = False):
+                lam: Optional[float] = None, count_nnz: Optional[bool] = None):
+        if count_nnz is None:
+            count_nnz = self.count_nnz
         self.epoch += 1
         b = self.epoch & 1
         s = _lib.stream_ptr()
         _lib.call("pcl_publish_flag", self._ready_table, self.world, self.rank, self.epoch, s)
-        h = DENSE_HANDLERS[handler or self.handler]
+        h, reg_lr, reg_lam = _dense_kind(handler or self.handler)
+        if lr is None:
+            lr = self.lr if reg_lr is None else reg_lr
+        if lam is None:
+            lam = self.lam if reg_lam is None else reg_lam
         if count_nnz:
             self.nnz.zero_()
         _lib.call("pcl_dense_bupdate", self.shard, self._delta_tables[b], self.Lp, self.S, self.world,
-                  self.rank, h, self.lr if lr is None else float(lr),
-                  self.lam if lam is None else float(lam), self.ready, self.epoch, self.timeout_ns,
+                  self.rank, h, float(lr), float(lam), self.ready, self.epoch, self.timeout_ns,
                   self.status, self._done_table, self.counter, self.nnz if count_nnz else None, s)
 
     def mark_written(self):
@@ -199,18 +243,27 @@ class DenseTable:
                   _lib.stream_ptr())
 
     def write(self, values: torch.Tensor):
-        """Owner-side initialisation from a full vector that every rank passes identically."""
+        """Collective initialisation from a full vector that every rank passes identically: each
+        owner stores its slice and publishes that as the next epoch, so the next ``read`` on any
+        rank waits (bounded) until every owner has written."""
         lo, hi = self.owned_range()
         self.shard.zero_()
         if hi > lo:
             self.shard[: hi - lo] = values[lo:hi].to(self.device, torch.float32)
+        self.mark_written()
+
+    def push(self, delta: torch.Tensor, scale: float = 1.0):
+        """One-sided update: this rank alone adds ``scale * delta`` (full length ``L``) into the
+        owners' shards by reductions over NVLink.  Nothing waits; other ranks see the result
+        after the next synchronisation (``paracel_sync`` or a clock commit)."""
+        _lib.check_cuda(delta, torch.float32, "delta")
+        if delta.numel() != self.L:
+            raise ValueError(f"delta has {delta.numel()} elements, the table {self.L}")
+        _lib.call("pcl_dense_push", self.theta_buf.ptr_table, delta, self.L, self.S, self.world,
+                  self.rank, float(scale), _lib.stream_ptr())
 
     def check(self):
-        st = self.status.cpu()
-        if int(st[0].item()) & 0xFFFFFFFF:
-            self.status.zero_()
-            raise RuntimeError(f"dense table wait timed out (wait id {int(st[1].item()) & 0xFFFFFFFF}: "
-                               f"expected {int(st[2])}, saw {int(st[3])})")
+        _lib.check_status(self.status, "dense table")
 
     def free(self):
         self.shard = None

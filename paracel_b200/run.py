@@ -175,11 +175,29 @@ def _dtr(comm, info, pt):
     return s
 
 
+def _l1(comm, info, pt, logistic=True):
+    """Sparse L1 logistic regression / Lasso.  The reference ships these as serial tools only
+    (tool/lr_l1_serial.cpp, tool/lasso_serial.cpp): without GPUs worker 0 runs the serial
+    shooting solver; with ``--gpu`` the proximal-gradient device path takes over."""
+    from .tool.lasso_serial import shooting_solver
+    if comm.get_rank() == 0:
+        s = shooting_solver(pt.check_parse("input", str), pt.parse("output", str), float(pt.get("lambda", 0.1)),
+                            int(pt.get("rounds", 100)), logistic=logistic)
+        s.solve()
+        s.dump_result()
+    comm.synchronize()
+    return None
+
+
+def _lasso(comm, info, pt):
+    return _l1(comm, info, pt, logistic=False)
+
+
 ALGORITHMS: Dict[str, Callable] = {
     "lr": _lr, "ridge": _ridge, "mf": _mf, "als": _als, "als_validate": _als, "svd": _svd, "gLDA": _lda,
     "lda": _lda, "kmeans": _kmeans, "pagerank": _pagerank, "mvv": _mvv, "wc": _wc,
     "sim_dense": _sim_dense, "ab_sim_dense": _sim_dense, "sim_sparse": _sim_sparse,
-    "adjust_ktop_sparse": _adjust_ktop, "dtr": _dtr,
+    "adjust_ktop_sparse": _adjust_ktop, "dtr": _dtr, "lr_l1": _l1, "lasso": _lasso,
 }
 
 

@@ -26,7 +26,8 @@ def _run(tmp_path, handler_file):
     cfg["update_file"] = cfg["filter_file"] = handler_file
     cfg_path = tmp_path / "cfg.json"
     cfg_path.write_text(json.dumps(cfg))
-    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""),
+               PARACEL_RUN_LOG=str(tmp_path / "paracelrun_log"))
     rc = subprocess.run([sys.executable, "-m", "paracel_b200.launch.prun", "-w", "2", "-p", "1", "-c",
                          str(cfg_path), "-m", "local", os.path.join(EX, "demo_app.py")],
                         env=env, cwd=ROOT, timeout=300).returncode

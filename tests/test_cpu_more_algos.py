@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from paracel_b200.launch.local import LocalJob
-from paracel_b200.testing import cpu_workers as W
+from workers import cpu_workers as W
 from paracel_b200.utils import dump as D
 
 

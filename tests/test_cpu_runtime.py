@@ -12,7 +12,7 @@ import pytest
 from paracel_b200.launch.cluster import (FAILED, FINISHED, GangScheduler, LocalAgent, SubmitScheduler,
                                          Task, TaskExecutor)
 from paracel_b200.launch.local import LocalJob
-from paracel_b200.testing import cpu_workers as W
+from workers import cpu_workers as W
 from paracel_b200.utils import checkpoint as C
 from paracel_b200.utils.metrics import MetricsLogger, PhaseTimer, get_logger
 

@@ -16,11 +16,23 @@ def _run(monkeypatch, tmp_path, algorithm, cfg):
     assert run.main([algorithm, "--server_info", "", "--cfg_file", str(p)]) == 0
 
 
+def _run_cpu(monkeypatch, tmp_path, algorithm, cfg):
+    """The host driver of the same executable, against parameter servers in this process."""
+    from paracel_b200 import run
+    from paracel_b200.ps.server import LocalServers
+    monkeypatch.setenv("PCL_USE_GPU", "0")
+    p = tmp_path / f"{algorithm}_cpu.json"
+    p.write_text(json.dumps(cfg))
+    with LocalServers(1) as srv:
+        assert run.main([algorithm, "--server_info", srv.info(), "--cfg_file", str(p)]) == 0
+
+
 def test_pagerank_driver_matches_power_iteration(monkeypatch, tmp_path):
     from paracel_b200.utils import dump as D
     edges = [(10, 20), (10, 30), (20, 30), (30, 10), (40, 30), (40, 10), (50, 40)]
     inp = tmp_path / "pr.txt"
-    inp.write_text("".join(f"{a},{b}\n" for a, b in edges) + "60,2147483648\n")
+    # a repeated line is still one edge (the containers of the reference keep adj[v][w])
+    inp.write_text("".join(f"{a},{b}\n" for a, b in edges) + "60,2147483648\n" + "10,20\n40,30\n")
     out = tmp_path / "pr_out"
     _run(monkeypatch, tmp_path, "pagerank", {"input": str(inp), "output": str(out) + "/", "rounds": 12,
                                               "damping_factor": 0.85})
@@ -34,6 +46,14 @@ def test_pagerank_driver_matches_power_iteration(monkeypatch, tmp_path):
     assert set(got) == {str(v) for v in nodes}
     for v in nodes:
         assert abs(got[str(v)] - pr[v]) < 1e-4
+    # and the host driver writes the same file for the same input
+    out_cpu = tmp_path / "pr_cpu"
+    _run_cpu(monkeypatch, tmp_path, "pagerank", {"input": str(inp), "output": str(out_cpu) + "/", "rounds": 12,
+                                                  "damping_factor": 0.85})
+    cpu = D.read_dict_scalar(os.path.join(str(out_cpu), "pagerank_0"))
+    assert set(cpu) == set(got)
+    for v in cpu:
+        assert abs(cpu[v] - got[v]) < 1e-4
 
 
 def test_kmeans_and_lr_drivers(monkeypatch, tmp_path):
@@ -87,7 +107,13 @@ def test_mf_and_lda_drivers(monkeypatch, tmp_path):
     assert len(W) == nu and len(H) == ni and all(1000 <= int(k) < 1000 + nu for k in W)
     assert len(next(iter(W.values()))) == 16
     miu = D.read_dict_scalar(os.path.join(str(out), "miu_0"))
-    assert abs(miu["rating_sz"] - 20000) < 0.5 and 2.5 < miu["miu"] < 3.5
+    # a repeated (user, item) line replaces the earlier rating, as in the host path
+    last = {}
+    for l in lines:
+        f = l.split()
+        last[(f[0], f[1])] = float(f[3])
+    assert abs(miu["rating_sz"] - len(last)) < 0.5
+    assert abs(miu["miu"] - sum(last.values()) / len(last)) < 1e-4
 
     vocab_a, vocab_b = [f"a{j}" for j in range(30)], [f"b{j}" for j in range(30)]
     docs = []
@@ -107,3 +133,99 @@ def test_mf_and_lda_drivers(monkeypatch, tmp_path):
         ws = [x.split(":")[0] for x in r.split("\t")[1].split("|") if x]
         pure += len({w[0] for w in ws}) == 1
     assert pure > 80      # (nearly empty topics list arbitrary words)
+
+
+def test_ridge_and_l1_drivers(monkeypatch, tmp_path):
+    rng = np.random.default_rng(2)
+    n, d = 3000, 6
+    A = rng.standard_normal((n, d))
+    w = rng.standard_normal(d)
+    yv = A @ w + 0.7 + 0.01 * rng.standard_normal(n)
+    tr = tmp_path / "ridge.csv"
+    np.savetxt(tr, np.concatenate([A, yv[:, None]], 1), delimiter=",", fmt="%.6f")
+    out = tmp_path / "ridge_out"
+    _run(monkeypatch, tmp_path, "ridge", {"training_input": str(tr), "output": str(out) + "/", "rounds": 60,
+                                           "alpha": 0.001, "beta": 0.0, "method": "ipm"})
+    theta = np.asarray([float(x) for x in open(out / "ridge_theta_0").read().strip().split("|")])
+    assert np.allclose(theta[1:], w, atol=0.05) and abs(theta[0] - 0.7) < 0.05
+    # sparse L1 logistic regression: the informative features survive, most others are zero
+    n, d = 6000, 40
+    X = (rng.random((n, d)) < 0.15).astype(float)
+    wt = np.zeros(d)
+    wt[:4] = [3.0, -3.0, 2.5, -2.5]
+    y = (rng.random(n) < 1 / (1 + np.exp(-(X @ wt)))).astype(float)
+    inp = tmp_path / "l1.csv"
+    np.savetxt(inp, np.concatenate([X, y[:, None]], 1), delimiter=",", fmt="%.1f")
+    out = tmp_path / "l1_out"
+    _run(monkeypatch, tmp_path, "lr_l1", {"input": str(inp), "output": str(out) + "/", "rounds": 300,
+                                           "eta": 2.0, "lambda": 0.01})
+    wv = np.asarray([float(x) for x in open(out / "lr_l1_weight_0").read().strip().split("|")])
+    assert wv.shape == (d,)
+    assert np.all(np.sign(wv[:4]) == np.sign(wt[:4])) and np.all(np.abs(wv[:4]) > 0.5)
+    assert (wv[4:] == 0).sum() >= 30
+
+
+def test_als_svd_sim_mvv_drivers_match_the_host_drivers(monkeypatch, tmp_path):
+    from paracel_b200.utils import dump as D
+    rng = np.random.default_rng(3)
+    # ---- ALS
+    nu, ni, k = 60, 40, 8
+    H = rng.normal(size=(ni, k))
+    fac = tmp_path / "H.txt"
+    fac.write_text("".join("%d\t%s\n" % (500 + j, "|".join("%.6f" % v for v in H[j])) for j in range(ni)))
+    pairs = {(int(rng.integers(0, nu)), int(rng.integers(0, ni))) for _ in range(900)}
+    rat = tmp_path / "rating.txt"
+    rat.write_text("".join("%d,%d,%.3f\n" % (100 + u, 500 + i, rng.uniform(1, 5)) for u, i in sorted(pairs)))
+    cfg = {"rating_input": str(rat), "factor_input": str(fac), "lambda": 0.2}
+    _run(monkeypatch, tmp_path, "als", dict(cfg, output=str(tmp_path / "als_gpu") + "/"))
+    _run_cpu(monkeypatch, tmp_path, "als", dict(cfg, output=str(tmp_path / "als_cpu") + "/"))
+    g = D.read_dict_vector(str(tmp_path / "als_gpu" / "W_0"))
+    c = D.read_dict_vector(str(tmp_path / "als_cpu" / "W_0"))
+    assert set(g) == set(c) and len(g) > 50
+    for key in c:
+        assert np.allclose(g[key], c[key], rtol=2e-3, atol=2e-3)
+    # ---- SVD
+    m, n = 80, 30
+    M = (rng.normal(size=(m, 3)) * np.array([8.0, 5.0, 3.0])) @ rng.normal(size=(3, n))
+    sv = tmp_path / "svd.txt"
+    sv.write_text("".join("%d,%d,%.6f\n" % (r, cc, M[r, cc]) for r in range(m) for cc in range(n)))
+    cfg = {"input": str(sv), "k": 3}
+    _run(monkeypatch, tmp_path, "svd", dict(cfg, output=str(tmp_path / "svd_gpu") + "/"))
+    sg = np.asarray([float(x) for x in open(tmp_path / "svd_gpu" / "SIGMA_0").read().replace("\n", ",").strip(",").split(",")])
+    assert np.allclose(sg, np.linalg.svd(M, compute_uv=False)[:3], rtol=2e-3)
+    U = D.read_dict_vector(str(tmp_path / "svd_gpu" / "U_0"))
+    V = D.read_dict_vector(str(tmp_path / "svd_gpu" / "V_0"))
+    rec = np.asarray([U[str(r)] for r in range(m)]) * sg[None, :] @ np.asarray([V[str(cc)] for cc in range(n)]).T
+    assert np.abs(rec - M).max() < 1e-2 * np.abs(M).max()
+    # ---- dense similarity
+    N, d = 90, 12
+    Xs = rng.normal(size=(N, d))
+    si = tmp_path / "sim.txt"
+    si.write_text("".join("%d,%s\n" % (1000 + j, ",".join("%.6f" % v for v in Xs[j])) for j in range(N)))
+    cfg = {"input": str(si), "topk": 4, "simbar": -1.0}
+    _run(monkeypatch, tmp_path, "sim_dense", dict(cfg, output=str(tmp_path / "sim_gpu") + "/"))
+    _run_cpu(monkeypatch, tmp_path, "sim_dense", dict(cfg, output=str(tmp_path / "sim_cpu") + "/"))
+    gl = sorted(open(tmp_path / "sim_gpu" / "result_0").read().splitlines())
+    cl = sorted(open(tmp_path / "sim_cpu" / "result_0").read().splitlines())
+    assert len(gl) == N == len(cl)
+
+    def parse(lines):
+        out = {}
+        for l in lines:
+            key, rest = l.split("\t")
+            out[key] = [(p.split(":")[0], float(p.split(":")[1])) for p in rest.split("|") if p]
+        return out
+    pg, pc = parse(gl), parse(cl)
+    for key in pc:
+        assert [a for a, _ in pg[key]] == [a for a, _ in pc[key]]
+        assert np.allclose([b for _, b in pg[key]], [b for _, b in pc[key]], atol=1e-4)
+    # ---- max vertex value
+    es, ed = rng.integers(1, 60, 150), rng.integers(1, 60, 150)
+    mv = tmp_path / "mvv.txt"
+    mv.write_text("".join("%d,%d\n" % (a, b) for a, b in zip(es, ed)))
+    cfg = {"input": str(mv)}
+    _run(monkeypatch, tmp_path, "mvv", dict(cfg, output=str(tmp_path / "mvv_gpu") + "/"))
+    _run_cpu(monkeypatch, tmp_path, "mvv", dict(cfg, output=str(tmp_path / "mvv_cpu") + "/"))
+    vg = D.read_dict_scalar(str(tmp_path / "mvv_gpu" / "vertex_val_0"))
+    vc = D.read_dict_scalar(str(tmp_path / "mvv_cpu" / "vertex_val_0"))
+    assert vg == vc and len(vg) > 20

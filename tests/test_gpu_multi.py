@@ -23,7 +23,7 @@ def _job(n):
 
 @needs2
 def test_symmetric_buffers_and_row_tables_across_ranks():
-    from paracel_b200.testing.gpu_workers import symm_and_rows
+    from workers.gpu_workers import symm_and_rows
     res = _job(2).run(symm_and_rows, timeout_s=300)
     for r in res:
         assert r["peer_vals"] == [1.0, 2.0]
@@ -32,7 +32,7 @@ def test_symmetric_buffers_and_row_tables_across_ranks():
 
 @needs2
 def test_device_ssp_clock_bound_and_timeout():
-    from paracel_b200.testing.gpu_workers import ssp_clock
+    from workers.gpu_workers import ssp_clock
     res = _job(2).run(ssp_clock, timeout_s=300)
     assert res[0]["max_ahead"] <= 2
     assert res[0]["timeout"] not in (None, "none")
@@ -41,7 +41,7 @@ def test_device_ssp_clock_bound_and_timeout():
 
 @needs2
 def test_mf_two_ranks_converges_like_one_rank():
-    from paracel_b200.testing.gpu_workers import mf_train
+    from workers.gpu_workers import mf_train
     args = (3000, 800, 200_000, 32, 5, 2)
     two = _job(2).run(mf_train, args, timeout_s=300)
     one = _job(1).run(mf_train, args, timeout_s=300)
@@ -54,7 +54,7 @@ def test_mf_two_ranks_converges_like_one_rank():
 @needs2
 @pytest.mark.parametrize("kernel", ["1sm", "2sm"])
 def test_fused_allgather_gemm_two_ranks(kernel):
-    from paracel_b200.testing.gpu_workers import fused_gather_gemm
+    from workers.gpu_workers import fused_gather_gemm
     res = _job(2).run(fused_gather_gemm, (1000, 64, 900, kernel), timeout_s=300)
     for r in res:
         assert r["err0"] < 5e-3 and r["err1"] < 5e-3, r
@@ -63,20 +63,20 @@ def test_fused_allgather_gemm_two_ranks(kernel):
 
 @needs2
 def test_dense_table_reduce_scatter_handler_two_ranks():
-    from paracel_b200.testing.gpu_workers import dense_table_two_ranks
+    from workers.gpu_workers import dense_table_two_ranks
     assert all(_job(2).run(dense_table_two_ranks, timeout_s=300))
 
 
 @needs2
 def test_sparse_l1lr_and_pagerank_two_ranks():
-    from paracel_b200.testing.gpu_workers import l1lr_and_pagerank_two_ranks
+    from workers.gpu_workers import l1lr_and_pagerank_two_ranks
     for ok_lr, ok_pr in _job(2).run(l1lr_and_pagerank_two_ranks, timeout_s=300):
         assert ok_lr and ok_pr
 
 
 @needs2
 def test_kmeans_allreduce_lda_two_ranks():
-    from paracel_b200.testing.gpu_workers import kmeans_allreduce_lda_two_ranks
+    from workers.gpu_workers import kmeans_allreduce_lda_two_ranks
     for r in _job(2).run(kmeans_allreduce_lda_two_ranks, timeout_s=300):
         assert r["allreduce"] and r["kmeans"], r
         assert r["lda_counts"][0] == r["lda_counts"][2] == r["lda_counts"][1], r
@@ -86,11 +86,34 @@ def test_kmeans_allreduce_lda_two_ranks():
 @needs2
 @pytest.mark.parametrize("pattern", ["fmap", "fsmap"])
 def test_device_loader_exchange_two_ranks(pattern):
-    from paracel_b200.testing.gpu_workers import device_exchange_ranks
+    from workers.gpu_workers import device_exchange_ranks
     res = _job(2).run(device_exchange_ranks, (pattern,), timeout_s=300)
     assert sum(r["n"] for r in res) == 100_000
     for r in res:
         assert r["triples"] and r["maps"] and r["idx"], r
+
+
+@needs2
+def test_paralg_api_on_device_tables_two_ranks():
+    from workers.gpu_workers import paralg_device_backend_two_ranks
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from paracel_b200.launch.local import LocalJob
+    for r in LocalJob(2, 1, backend="cpu:gloo,cuda:nccl").run(paralg_device_backend_two_ranks, timeout_s=300):
+        assert r == {"row_read": True, "row_in_owner_hbm": True, "dense_equals_host": True,
+                     "batch_push": True, "filter_view": True}, r
+
+
+@needs2
+def test_first_read_of_a_collectively_written_key_waits_for_every_owner():
+    from workers.gpu_workers import dense_linear_first_read_sees_theta0
+    assert all(_job(2).run(dense_linear_first_read_sees_theta0, timeout_s=300))
+
+
+@needs2
+def test_als_svd_similarity_mvv_two_ranks():
+    from workers.gpu_workers import suite_models_two_ranks
+    for r in _job(2).run(suite_models_two_ranks, timeout_s=600):
+        assert r["als"] and r["svd_sigma"] and r["svd_recon"] and r["sim_dense"] and r["mvv"], r
 
 
 @needs2
@@ -108,7 +131,8 @@ def test_launcher_gpu_switch_runs_pagerank_on_two_gpus(tmp_path):
     cfg.write_text(json.dumps({"input": str(inp), "output": str(tmp_path / "out") + "/", "rounds": 6,
                                "damping_factor": 0.85}))
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=root)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=root,
+               PARACEL_RUN_LOG=str(tmp_path / "paracelrun_log"))
     rc = subprocess.run([sys.executable, "-m", "paracel_b200.launch.prun", "-w", "2", "-p", "1", "-c", str(cfg),
                          "-m", "local", "--gpu", "pagerank"], env=env, cwd=root, timeout=300).returncode
     assert rc == 0

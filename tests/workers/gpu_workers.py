@@ -354,3 +354,187 @@ def device_exchange_ranks(comm, server_info, pattern):
     ok_maps = bool(torch.equal(rm, torch.unique(A[in_row])) and torch.equal(cm, torch.unique(B[in_col])))
     ok_idx = bool(torch.equal(rm[ri], a2) and torch.equal(cm[ci], b2))
     return {"triples": ok_triples, "maps": ok_maps, "idx": ok_idx, "n": int(a2.numel())}
+
+
+def paralg_device_backend_two_ranks(comm, server_info):
+    """The public paralg calls on keys of device tables, from two ranks: a row written by one
+    rank is read by the other out of the owner's HBM; updates of a dense key from both ranks give
+    what the host parameter server gives for the same calls."""
+    from paracel_b200.paralg import paralg
+    rank, world = comm.get_rank(), comm.get_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    pt = paralg(server_info, comm, backend="gpu", device=dev)
+    out = {}
+    W = pt.paracel_row_table(1000, 8, prefix="W_", handler="mf_fac_updater")
+    L = 10007
+    pt.paracel_dense_table("theta", L, handler="lr_theta_update")
+    row = [float(j) + 0.5 for j in range(8)]
+    if rank == 0:
+        pt.paracel_write("W_123", row)
+    pt.paracel_sync()
+    got = pt.paracel_read("W_123").tolist()
+    out["row_read"] = got == row
+    owner = 123 % world
+    if rank == owner:
+        out["row_in_owner_hbm"] = W.table.shard[123 // world].tolist() == row
+    else:
+        out["row_in_owner_hbm"] = float(W.table.shard[123 // world].abs().sum()) == 0.0
+    # dense key: one-sided and collective updates from both ranks against the host server
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    theta0 = torch.randn(L, device=dev, generator=g)
+    g.manual_seed(100 + rank)
+    d1 = torch.randn(L, device=dev, generator=g)
+    d2 = torch.randn(L, device=dev, generator=g)
+    pt.paracel_write("theta", theta0)
+    if rank == 0:
+        pt.paracel_write("theta_host", theta0.double().cpu().tolist())
+    pt.paracel_sync()
+    pt.paracel_bupdate("theta", d1, "", "lr_theta_update")                    # one-sided, like the RPC
+    pt.paracel_bupdate("theta_host", d1.double().cpu().tolist(), "", "lr_theta_update")
+    pt.paracel_sync()
+    pt.paracel_bupdate("theta", d2, "", "lr_theta_update", collective=True)   # fused reduce-scatter
+    pt.paracel_bupdate("theta_host", d2.double().cpu().tolist(), "", "lr_theta_update")
+    pt.paracel_sync()
+    dev_val = pt.paracel_read("theta").double().cpu()
+    host_val = torch.tensor(pt.paracel_read("theta_host"), dtype=torch.float64)
+    out["dense_equals_host"] = bool(torch.allclose(dev_val, host_val, rtol=1e-5, atol=1e-5))
+    # key batch from both ranks + filter view
+    ids = torch.arange(rank, 1000, 7, device=dev)
+    kb = pt.paracel_keys(W, ids)
+    pt.paracel_bupdate_multi(kb, torch.ones(ids.numel(), 8, device=dev), "", "mf_fac_updater")
+    pt.paracel_sync()
+    allrows = pt.paracel_read_multi(pt.paracel_keys(W, torch.arange(1000, device=dev)))
+    cnt = torch.zeros(1000, device=dev)
+    for r in range(world):
+        cnt[torch.arange(r, 1000, 7, device=dev)] += 1
+    exp = cnt[:, None].expand(1000, 8).clone()
+    exp[123] += torch.tensor(row, device=dev)
+    out["batch_push"] = bool(torch.allclose(allrows, exp))
+    d = pt.paracel_read_special("", "mf_W_filter")
+    out["filter_view"] = len(d) == 1000 and d["W_123"] == exp[123].tolist()
+    pt.paracel_check()
+    pt.close()
+    return out
+
+
+def dense_linear_first_read_sees_theta0(comm, server_info):
+    """A non-zero initial theta written collectively is what the first read returns on every
+    rank, although one rank writes its slice a second later and nobody calls a barrier."""
+    from paracel_b200.models.linear_gpu import DenseLinearGpu
+    rank = comm.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    d = 4099
+    g = torch.Generator().manual_seed(3)
+    theta0 = torch.rand(d, generator=g).to(dev) + 1.0
+    X = torch.randn(64, d, generator=g)
+    y = (torch.rand(64, generator=g) < 0.5).float()
+    m = DenseLinearGpu(d, eta=0.1)
+    if rank == 1:
+        time.sleep(1.0)
+    m.load(X, y, theta0=theta0)
+    first = m.paracel_read("theta").clone()
+    ok = bool(torch.equal(first, theta0))
+    m.step()
+    m.paracel_sync()
+    m.paracel_check()
+    m.free()
+    return ok
+
+
+def suite_models_two_ranks(comm, server_info):
+    """ALS, SVD, dense similarity and max-vertex-value on 2 ranks against fp64 NumPy oracles."""
+    import numpy as np
+    from paracel_b200.models.als_gpu import AlsGpu
+    from paracel_b200.models.mvv_gpu import MvvGpu
+    from paracel_b200.models.similarity_gpu import SimDenseGpu
+    from paracel_b200.models.svd_gpu import SvdGpu
+    rank, world = comm.get_rank(), comm.get_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    rng = np.random.default_rng(7)
+    out = {}
+    # ---- ALS: H rows live in the table, every rank solves the users u % world == rank
+    nu, ni, k, lam = 300, 120, 24, 0.3
+    H = rng.normal(size=(ni, k))
+    uu = rng.integers(0, nu, 6000)
+    ii = rng.integers(0, ni, 6000)
+    _, first = np.unique(uu * ni + ii, return_index=True)
+    uu, ii = uu[first], ii[first]
+    rr = rng.uniform(1, 5, uu.size)
+    als = AlsGpu(nu, ni, k, lam)
+    mine = uu % world == rank
+    flo, fhi = rank * ni // world, (rank + 1) * ni // world        # my slice of the factor file
+    als.load(torch.tensor(uu[mine]), torch.tensor(ii[mine]), torch.tensor(rr[mine], dtype=torch.float32),
+             torch.arange(flo, fhi), torch.tensor(H[flo:fhi], dtype=torch.float32))
+    als.solve()
+    Wd = als.paracel_read_multi(als.paracel_keys(als.W_tab, torch.arange(nu, device=dev)))[:, :k].double().cpu().numpy()
+    ok = True
+    for u in range(nu):
+        sel = uu == u
+        if not sel.any():
+            continue
+        Hs = H[ii[sel]]
+        w = np.linalg.solve(Hs.T @ Hs + lam * np.eye(k), Hs.T @ rr[sel])
+        ok = ok and np.allclose(Wd[u], w, rtol=2e-3, atol=2e-3)
+    out["als"] = bool(ok)
+    out["als_rmse"] = als.cal_rmse()
+    als.free()
+    # ---- SVD: low-rank + noise matrix, rows split over the ranks
+    m, n, kk = 400, 90, 4
+    A = (rng.normal(size=(m, kk)) * np.array([9.0, 6.0, 4.0, 2.5])) @ rng.normal(size=(kk, n)) + 0.01 * rng.normal(size=(m, n))
+    A[rng.random((m, n)) < 0.3] = 0.0
+    rows = np.arange(rank, m, world)
+    sub = A[rows]
+    nzr, nzc = np.nonzero(sub)
+    ptr = np.zeros(rows.size + 1, dtype=np.int64)
+    np.cumsum(np.bincount(nzr, minlength=rows.size), out=ptr[1:])
+    svd = SvdGpu(n, kk, iters=25, oversample=8, seed=1)
+    svd.load(torch.tensor(ptr), torch.tensor(nzc, dtype=torch.int32), torch.tensor(sub[nzr, nzc], dtype=torch.float32))
+    svd.solve()
+    S_ref = np.linalg.svd(A, compute_uv=False)[:kk]
+    out["svd_sigma"] = bool(np.allclose(svd.sigma.numpy(), S_ref, rtol=2e-3))
+    U = svd.U.double().cpu().numpy()
+    V = svd.V.double().cpu().numpy()
+    recon = (U * svd.sigma.numpy()[None, :]) @ V.T
+    Ur, Sr, Vr = np.linalg.svd(A, full_matrices=False)
+    best = (Ur[:, :kk] * Sr[:kk]) @ Vr[:kk]
+    out["svd_recon"] = bool(np.abs(recon - best[rows]).max() < 2e-2 * np.abs(best).max())
+    svd.free()
+    # ---- dense similarity: every rank holds a block of the rows
+    N, d, ktop = 500, 20, 5
+    Xs = rng.normal(size=(N, d))
+    ids = rng.permutation(10_000)[:N]
+    lo, hi = rank * N // world, (rank + 1) * N // world
+    sim = SimDenseGpu(d, ktop, simbar=-1.0)
+    sim.load(torch.tensor(ids[lo:hi]), torch.tensor(Xs[lo:hi], dtype=torch.float32))
+    sim.solve()
+    Xn = Xs / np.linalg.norm(Xs, axis=1, keepdims=True)
+    S = Xn @ Xn.T
+    np.fill_diagonal(S, -np.inf)
+    ok = True
+    for a in range(lo, hi):
+        want = np.argsort(-S[a])[:ktop]
+        got = sim.result[int(ids[a])]
+        ok = ok and [g_[0] for g_ in got] == [int(ids[j]) for j in want]
+        ok = ok and np.allclose([g_[1] for g_ in got], S[a, want], atol=1e-4)
+    out["sim_dense"] = bool(ok)
+    sim.free()
+    # ---- max vertex value: edges held by the owner of their source
+    nv, ne = 400, 900
+    es, ed = rng.integers(0, nv, ne), rng.integers(0, nv, ne)
+    val = {int(v): float(v) for v in np.unique(es)}
+    changed = True
+    while changed:                                   # values flow along edges from source to target
+        changed = False
+        for a, b in zip(es.tolist(), ed.tolist()):
+            if b in val and val[a] > val[b]:
+                val[b] = val[a]
+                changed = True
+    mv = MvvGpu(nv)
+    mine = es % world == rank
+    mv.load_edges(torch.tensor(es[mine]), torch.tensor(ed[mine]))
+    mv.solve()
+    got = dict(zip(mv.lv.cpu().tolist(), mv.val.cpu().tolist()))
+    out["mvv"] = all(got[v] == val[v] for v in got) and len(got) > 0
+    mv.free()
+    return out
