@@ -58,7 +58,7 @@ def parse_args():
     ap.add_argument("--phases", action="store_true",
                     help="after the timed steps run two extra rounds with per-phase device timing")
     ap.add_argument("--no-balance", action="store_true")
-    ap.add_argument("--hot-mix", type=float, default=0.125)
+    ap.add_argument("--hot-mix", type=float, default=-1.0, help="concurrency damping (negative: the model's default)")
     ap.add_argument("--sgd-blocks", type=int, default=0)
     ap.add_argument("--hot-rows", type=int, default=106)
     ap.add_argument("--variant", type=int, default=0, help="SGD kernel: 0 automatic (16 lanes per rating at rank 128), 1: 32 lanes per rating, "
@@ -67,6 +67,8 @@ def parse_args():
     ap.add_argument("--zipf-s", type=float, default=1.1)
     ap.add_argument("--heldout", type=int, default=2_000_000,
                     help="pairs drawn like the training pairs but never trained on (0: skip)")
+    ap.add_argument("--grid", default="", help="rank grid ROWSxCOLS of the rating partition (default: the "
+                    "most square factorisation)")
     ap.add_argument("--overlap-push", type=int, default=-1,
                     help="1: push + commit on a side stream under the next SGD pass; 0: in line; "
                          "-1: the model's default")
@@ -116,9 +118,10 @@ def main():
     t_setup = time.time()
     model = Model(args.users, args.items, k=args.rank, alpha=args.alpha, beta=args.beta,
                   rounds=total_rounds, staleness=args.staleness, ssp=True, seed=args.seed,
-                  hot_mix=args.hot_mix, sgd_blocks=args.sgd_blocks, device=dev,
+                  hot_mix=(args.hot_mix if args.hot_mix >= 0 else None), sgd_blocks=args.sgd_blocks, device=dev,
                   hot_rows=args.hot_rows, chunks_per_flush=args.chunks_per_flush,
-                  variant=args.variant)
+                  variant=args.variant,
+                  **({"grid": tuple(int(x) for x in args.grid.split("x"))} if args.grid and args.impl == "ours" else {}))
     if args.overlap_push >= 0 and hasattr(model, "overlap_push"):
         model.overlap_push = bool(args.overlap_push)
 

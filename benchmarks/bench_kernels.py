@@ -1,9 +1,10 @@
 #!/usr/bin/env python
 """Micro-benchmarks of the single-GPU algorithm kernels against stock PyTorch ops doing the same
-job: batched ALS solve, k-means accumulate, Gram matrix, device ball-tree search, dense LR gradient.  CUDA events,
-3 warm-ups, L2 flushed between timed launches, one JSON line per kernel.
+job: batched ALS solve, k-means accumulate, Gram matrix, device ball-tree search, dense LR gradient,
+the CSR products of the SVD, blockwise similarity with top-k.  CUDA events, 3 warm-ups, L2 flushed
+between timed launches, one JSON line per kernel.
 
-    python benchmarks/bench_kernels.py [--kernel als|kmeans|gram|balltree|dense_grad|all]
+    python benchmarks/bench_kernels.py [--kernel als|kmeans|gram|balltree|dense_grad|spmm|sim_topk|all]
 """
 import argparse
 import json
@@ -141,13 +142,75 @@ def bench_dense_grad(flush):
             "speedup": ms_ref / ms}
 
 
+def bench_spmm(flush):
+    """A.H and A^T.W for a CSR matrix with 64-wide dense factors against torch.sparse.mm."""
+    from paracel_b200.ops.svd import spmm_csr, spmm_csr_t
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(2)
+    m, n, per_row, K = 2_000_000, 500_000, 40, 64
+    cols = torch.randint(0, n, (m * per_row,), device=dev, generator=g, dtype=torch.int32)
+    vals = torch.rand(m * per_row, device=dev, generator=g)
+    ptr = torch.arange(0, m * per_row + 1, per_row, device=dev, dtype=torch.int64)
+    H = torch.randn(n, K, device=dev, generator=g)
+    W = torch.randn(m, K, device=dev, generator=g)
+    out_w = torch.empty(m, K, device=dev)
+    out_h = torch.zeros(n, K, device=dev)
+    ms = timeit(lambda: spmm_csr(ptr, cols, vals, H, out_w), flush)
+
+    def ours_t():
+        out_h.zero_()
+        spmm_csr_t(ptr, cols, vals, W, out_h)
+    ms_t = timeit(ours_t, flush)
+    A = torch.sparse_csr_tensor(ptr, cols.long(), vals, (m, n))
+    At = A.to_sparse_coo().t().coalesce().to_sparse_csr()
+    ms_ref = timeit(lambda: torch.sparse.mm(A, H), flush)
+    ms_ref_t = timeit(lambda: torch.sparse.mm(At, W), flush)
+    nnz = m * per_row
+    return {"kernel": "spmm_csr / spmm_csr_t", "rows": m, "cols": n, "nnz": nnz, "K": K, "ms": ms, "ms_t": ms_t,
+            "gflops": 2.0 * nnz * K / ms / 1e6, "gflops_t": 2.0 * nnz * K / ms_t / 1e6,
+            "torch_sparse_mm_ms": ms_ref, "torch_sparse_mm_t_ms_pretransposed": ms_ref_t,
+            "speedup": ms_ref / ms, "speedup_t": ms_ref_t / ms_t}
+
+
+def bench_sim_topk(flush):
+    """Similarity of 16 k rows against 131 k rows (dim 128) with a running top-20: the 3xTF32
+    tcgen05 GEMM + top-k kernel against torch.matmul (fp32) + torch.topk on the same tiles."""
+    from paracel_b200.ops.gemm import gemm_nt, split3
+    from paracel_b200.ops.misc import RunningTopK
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(3)
+    ma, nb, d, k = 16384, 131072, 128, 20
+    A = torch.nn.functional.normalize(torch.randn(ma, d, device=dev, generator=g))
+    B = torch.nn.functional.normalize(torch.randn(nb, d, device=dev, generator=g))
+    ids_a = torch.arange(ma, device=dev) + 10_000_000
+    ids_b = torch.arange(nb, device=dev)
+    A3, B3 = split3(A, False), split3(B, True)
+    S = torch.empty(ma, nb, device=dev)
+
+    def ours():
+        from paracel_b200.ops.gemm import _launch
+        _launch(A3, B3, S, 0, None, None, None)
+        t = RunningTopK(ids_a, k, 0.0)
+        t.update(S, ids_b)
+        return t
+    torch.backends.cuda.matmul.allow_tf32 = False
+
+    def ref():
+        return torch.topk(A @ B.T, k, dim=1)
+    ms, ms_ref = timeit(ours, flush), timeit(ref, flush)
+    return {"kernel": "similarity 3xTF32 GEMM + top-k", "rows_a": ma, "rows_b": nb, "dim": d, "k": k, "ms": ms,
+            "tflops_fp32_equiv": 2.0 * ma * nb * d / ms / 1e9, "torch_fp32_matmul_topk_ms": ms_ref,
+            "speedup": ms_ref / ms}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="all", choices=["all", "als", "kmeans", "gram", "balltree", "dense_grad"])
+    ap.add_argument("--kernel", default="all", choices=["all", "als", "kmeans", "gram", "balltree", "dense_grad", "spmm",
+                                                         "sim_topk"])
     args = ap.parse_args()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     table = {"als": bench_als, "kmeans": bench_kmeans, "gram": bench_gram, "balltree": bench_balltree,
-             "dense_grad": bench_dense_grad}
+             "dense_grad": bench_dense_grad, "spmm": bench_spmm, "sim_topk": bench_sim_topk}
     for name, fn in table.items():
         if args.kernel in ("all", name):
             print(json.dumps(fn(flush)))

@@ -20,11 +20,15 @@
 //   warp 1      tensor-memory allocation (both CTAs); in the leader one lane issues
 //               the M256 N256 K8 MMAs and commits to the barriers of both CTAs
 //   warps 2-9   epilogue on the CTA's own accumulator half, two warps per tensor-memory
-//               sub-partition (each takes 128 of the 256 columns): tcgen05.ld, transpose
-//               through swizzled shared memory, coalesced row stores (or arg-min); the
-//               accumulator buffer is released as soon as its last chunk is in registers.
-//               With K = 512 a tile's MMAs take about 4 us; four epilogue warps needed
-//               about 8 us per tile and held the tensor cores back.
+//               sub-partition (each takes 128 of the 256 columns): tcgen05.ld of the next
+//               32 x 32 chunk is in flight while the current one is written, with the
+//               128-byte swizzle, into one of the warp's two staging buffers and handed to a
+//               bulk tensor store (cp.async.bulk.tensor shared -> global, local memory, no
+//               multicast form exists for stores), which clips at the edges of C; or the
+//               arg-min.  The accumulator buffer is released as soon as its last chunk is in
+//               registers.  With K = 512 a tile's MMAs take about 4 us; four epilogue warps
+//               with per-row global stores needed about 8 us per tile and held the tensor
+//               cores back.
 // Every wait has a time limit; on expiry the status record is written, both
 // CTAs of the pair are told to leave, tensor memory is freed and the kernel ends.
 #include <cuda.h>
@@ -44,7 +48,8 @@ constexpr int A_BYTES = HM * BK * 4;
 constexpr int B_BYTES = HN * BK * 4;
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
-constexpr int EPI_BYTES = EPI_WARPS * 32 * 128;  // one 32 x 32 fp32 chunk per epilogue warp
+constexpr int EPI_BUFS = 1;  // staging buffers per epilogue warp (4 KB each)
+constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * 32 * 128;
 constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr unsigned long long WAIT_NS = 2000000000ull;  // 2 s per wait
 
@@ -153,13 +158,12 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
                : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
-  uint32_t r[32];
+// tcgen05.ld without the wait: the 32 registers are valid after tmem_ld_wait(r)
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
-      "tcgen05.wait::ld.sync.aligned;"
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
         "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
         "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
@@ -167,8 +171,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// wait for the loads issued so far; naming the registers keeps their uses behind the wait
+__device__ __forceinline__ void tmem_ld_wait(uint32_t* r) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+        "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]),
+        "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]),
+        "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]),
+        "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+      :
+      : "memory");
+}
+
+// 32 x 32 fp32 box from shared memory (128-byte swizzled) to C at (column x, row y); rows and
+// columns beyond the tensor's extent are dropped by the copy engine
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
 __device__ __forceinline__ void report(PclStatus* st, int rank, int wait_id, long long expected,
@@ -209,7 +233,7 @@ __device__ __forceinline__ void abort_pair(volatile int* abort_flag, uint32_t pe
 
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     Gemm2Args a) {
+                     const __grid_constant__ CUtensorMap tmC, Gemm2Args a) {
   extern __shared__ uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = (a.N + TN - 1) / TN;
@@ -406,7 +430,8 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     const int sub = warp & 3;                 // tensor-memory sub-partition of this warp
     const int half = (warp - 2) >> 2;         // which 128 of the tile's 256 columns
     constexpr int HC = TN / 2;                // columns per epilogue warp
-    float* stg = reinterpret_cast<float*>(sE + (warp - 2) * 4096);
+    float* stg = reinterpret_cast<float*>(sE + (warp - 2) * (EPI_BUFS * 4096));
+    unsigned stores = 0;                                              // bulk stores issued by this warp
     const uint32_t tempty_leader0 = map_to_cta(smem_u32(tempty), 0);
     int acc = 0;
     uint32_t acc_phase[2] = {0, 0};
@@ -439,36 +464,45 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           }
           __syncwarp();
         }
-#pragma unroll 1
+        uint32_t rv[2][32];
+        tmem_ld32_issue(t0 + (uint32_t)(half * HC), rv[0]);
+#pragma unroll
         for (int c = 0; c < HC / 32; ++c) {
-          float v[32];
-          tmem_ld32(t0 + (uint32_t)(half * HC + c * 32), v);   // load and wait in one statement
-          if (c + 1 == HC / 32) {
+          uint32_t* cur = rv[c & 1];
+          tmem_ld_wait(cur);
+          if (c + 1 < HC / 32) {
+            tmem_ld32_issue(t0 + (uint32_t)(half * HC + (c + 1) * 32), rv[(c + 1) & 1]);
+          } else {
             // the last chunk is in registers: hand the accumulator buffer back before its stores
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty_leader0 + (uint32_t)(acc * 8));
           }
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(cur[j]);
           const int n0 = nt * TN + half * HC + c * 32;
           if (n0 >= a.N) continue;
           if (a.epi == 0) {
-            if (n0 + 32 <= a.N && vec_ok) {
-              // transpose through shared memory: lane r wrote row r; afterwards 8 lanes cover
-              // the 128 bytes of one row, so one store instruction writes 4 full lines
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<float4*>(stg + lane * 32 + ((q ^ (lane & 7)) << 2)) =
-                    make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-              __syncwarp();
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int r = 4 * i + (lane >> 3);
-                const int q = lane & 7;
-                const float4 x = *reinterpret_cast<const float4*>(stg + r * 32 + ((q ^ (r & 7)) << 2));
-                if (row_base + r < a.M)
-                  *reinterpret_cast<float4*>(a.C + (long long)(row_base + r) * a.ldc + n0 + 4 * q) = x;
+            if (vec_ok) {
+              // lane r writes accumulator row r into the staging buffer with the 128-byte swizzle
+              // (16-byte chunk q of row r sits at chunk q ^ (r & 7)); one bulk tensor store then
+              // moves the 32 x 32 box to C.  The buffer that the store before the previous one
+              // read is free once at most one store is still reading.
+              float* buf = stg + (stores % EPI_BUFS) * 1024;
+              if (lane == 0) {
+                if (EPI_BUFS == 1) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
               }
               __syncwarp();
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(buf + lane * 32 + ((q ^ (lane & 7)) << 2)) =
+                    make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) tma_store_2d(&tmC, smem_u32(buf), n0, row_base);
+              ++stores;
             } else if (row < a.M) {
               float* dst = a.C + (long long)row * a.ldc + n0;
               for (int j = 0; j < 32; ++j)
@@ -511,6 +545,9 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         a.row_arg[(long long)half * a.M + row] = best_n;
       }
     }
+    // the staging buffers must stay intact until the copy engine has read them
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
   }
 
   // nobody leaves while the peer may still read this CTA's shared memory or signal its barriers
@@ -539,6 +576,20 @@ encode_fn_t get_encode2() {
       fn = (encode_fn_t)p;
   }
   return fn;
+}
+
+// map of C (M rows, N columns, row stride ldc floats) for the 32 x 32 boxes of the epilogue
+int make_map_c(CUtensorMap* map, const float* ptr, long long M, long long N, long long ldc) {
+  encode_fn_t enc = get_encode2();
+  if (enc == nullptr) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
 int make_map2(CUtensorMap* map, const float* ptr, long long rows, long long K, int box_rows) {
@@ -571,10 +622,15 @@ PCL_API int pcl_gemm_tf32_2sm(const float* A, float* b_stage, float* C, int M, i
   if (epi == 0 && C == nullptr) return (int)cudaErrorInvalidValue;
   if (epi == 1 && (bnorm == nullptr || row_min == nullptr || row_arg == nullptr))
     return (int)cudaErrorInvalidValue;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
   int rc = make_map2(&tmA, A, M, K, HM);
   if (rc) return rc;
   rc = make_map2(&tmB, b_stage, N, K, HN);
+  if (rc) return rc;
+  // bulk tensor stores need a 16-byte aligned base and row stride; otherwise (and for the arg-min
+  // epilogue) the map is a stand-in over A that the kernel never uses
+  const bool c_ok = (epi == 0) && ((ldc & 3) == 0) && ((((uintptr_t)C) & 15) == 0);
+  rc = c_ok ? make_map_c(&tmC, C, M, N, ldc) : make_map2(&tmC, A, M, K, HM);
   if (rc) return rc;
   Gemm2Args a;
   a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.epi = epi;
@@ -617,7 +673,7 @@ PCL_API int pcl_gemm_tf32_2sm(const float* A, float* b_stage, float* C, int M, i
   const long long n_items = (epi == 0) ? (long long)m_tiles * ((N + TN - 1) / TN) : (long long)m_tiles;
   if (mma_pairs > n_items) mma_pairs = (int)n_items;
   cfg.gridDim = dim3((unsigned)(a.gather_ctas + 2 * mma_pairs), 1, 1);
-  e = cudaLaunchKernelEx(&cfg, gemm_tf32_2sm_kernel, tmA, tmB, a);
+  e = cudaLaunchKernelEx(&cfg, gemm_tf32_2sm_kernel, tmA, tmB, tmC, a);
   if (e != cudaSuccess) return (int)e;
   return pcl_last_error();
 }

@@ -122,12 +122,12 @@ def grid_rank(u: torch.Tensor, i: torch.Tensor, ugrp: torch.Tensor, igrp: torch.
 class MfSgdGpu(paralg):
     def __init__(self, n_users: int, n_items: int, k: int = 128, alpha: float = 0.005,
                  beta: float = 0.02, rounds: int = 1, staleness: int = 2, ssp: bool = True,
-                 group=None, device=None, seed: int = 0, hot_mix: float = 0.125,
+                 group=None, device=None, seed: int = 0, hot_mix: Optional[float] = None,
                  sgd_blocks: int = 0, timeout_s: float = 5.0, hot_rows: int = 106,
                  chunks_per_flush: int = 8, variant: int = 0, compact: bool = True,
                  comm=None, hosts_dct_str=None, output: str = "", user_names=None,
                  item_names=None, update_funcs=None, flush_scale: float = 0.0,
-                 flush_mode: str = "uniform"):
+                 flush_mode: str = "uniform", grid=None):
         super().__init__(hosts_dct_str, comm, output, int(rounds), int(staleness) if ssp else 0,
                          bool(ssp), wait_timeout_s=timeout_s, backend="gpu", device=device,
                          group=group)
@@ -146,7 +146,8 @@ class MfSgdGpu(paralg):
         # 1.0 damps a row by its full expected concurrency; 0.125 was the best of a sweep
         # (1, 0.5, 0.25, 0.125, 0.06, 0.03) of held-out RMSE per epoch on Zipf(1.1) ratings against
         # the sequential fp64 pass, and values below 0.06 start to oscillate.
-        self.hot_mix = float(hot_mix)
+        # (That sweep ran the 16-lanes-per-rating kernel; the other kernels keep 1.0 unless told.)
+        self._hot_mix_arg = hot_mix
         # weight of a CTA's accumulated hot-row delta when it is mixed into the global row
         # (<= 0: 1 / number of CTAs, the plain average of the replicas)
         self.flush_scale = float(flush_scale)
@@ -162,13 +163,18 @@ class MfSgdGpu(paralg):
         self.g8 = (self.D == 128 and self.variant == 2)
         # variant 3 (D = 128): sixteen lanes per rating, two chunks per warp, 1 CTA of 640 threads per SM
         self.h16 = (self.D == 128 and self.variant in (0, 3))
+        self.hot_mix = float(self._hot_mix_arg) if self._hot_mix_arg is not None else (0.125 if self.h16 else 1.0)
         one_cta = self.g8 or self.h16
         self.sgd_blocks = int(sgd_blocks) if sgd_blocks > 0 else (148 if one_cta else 148 * 2)
         self.h16_threads = int(os.environ.get("PCL_MF_H16_THREADS", "640"))
         self.warps_per_block = 64 if self.g8 else (self.h16_threads // 16 if self.h16 else 16)   # chunks in flight per CTA
         self.hot_rows = int(hot_rows)
         self.chunks_per_flush = int(chunks_per_flush)
-        self.npx, self.npy = npfact2d(self.world)
+        # rank grid of the fsmap pattern: a user's ratings live on one grid row (npy ranks share
+        # the user's row of W), an item's on one grid column (npx ranks share its row of H)
+        self.npx, self.npy = npfact2d(self.world) if grid is None else (int(grid[0]), int(grid[1]))
+        if self.npx * self.npy != self.world:
+            raise ValueError(f"grid {self.npx} x {self.npy} does not match {self.world} workers")
         self.px, self.py = self.rank // self.npy, self.rank % self.npy
         # parameter tables (shards in HBM) behind the reference's key names
         self.user_names, self.item_names = user_names, item_names

@@ -21,6 +21,8 @@ def als_solve(user_ptr: torch.Tensor, item_idx: torch.Tensor, rating: torch.Tens
     dev = H.device
     H = H.contiguous().float()
     n_users, k = user_ptr.numel() - 1, H.shape[1]
+    # the kernel gathers rows of H by these indices without looking at them again
+    _lib.validate_ids(item_idx.contiguous(), 0, H.shape[0], "ALS ratings (item rows)")
     K = _kpad(k)
     W = torch.zeros(n_users, k, device=dev)
     cnt = (user_ptr[1:] - user_ptr[:-1])

@@ -206,7 +206,17 @@ def main(argv=None) -> int:
     ap.add_argument("algorithm", choices=sorted(ALGORITHMS))
     ap.add_argument("--server_info", required=True)
     ap.add_argument("--cfg_file", required=True)
+    ap.add_argument("--resume", default="", help="checkpoint directory to continue from (device drivers)")
+    ap.add_argument("--checkpoint", default="", help="directory to write a checkpoint to when the run ends")
+    ap.add_argument("--metrics", action="store_true", help="write <output>/metrics.jsonl and a phase trace")
     a = ap.parse_args(argv)
+    # the drivers see these through the environment, like the launcher's --gpu switch
+    if a.resume:
+        os.environ["PCL_RESUME"] = a.resume
+    if a.checkpoint:
+        os.environ["PCL_CHECKPOINT"] = a.checkpoint
+    if a.metrics:
+        os.environ["PCL_METRICS"] = "1"
     env = main_env()
     try:
         comm = Comm()

@@ -44,7 +44,7 @@ def _partition(comm, pattern):
 def _my_lines(comm, pattern) -> List[str]:
     """The lines of this rank's byte range of the input (line boundaries fixed up)."""
     r = comm.get_rank()
-    return [l for l in _partition(comm, pattern).load_lines(r, r + 1) if l]
+    return [l for l in _partition(comm, pattern).load_blocks(r, r + 1) if l]
 
 
 def _my_triples(comm, pattern, seps: str, drop_fields: Sequence[int] = ()) -> Tuple[np.ndarray, ...]:
@@ -98,12 +98,35 @@ def _dense_rows(lines: List[str], seps: str = ",") -> np.ndarray:
     return np.asarray(core().parse_dense_rows(lines, seps), dtype=np.float32) if lines else np.zeros((0, 0), np.float32)
 
 
+def _begin(m, pt=None):
+    """Run options common to the device drivers: ``--metrics`` (or the config key ``metrics``)
+    switches on metrics.jsonl and the phase trace, ``--resume DIR`` continues from a checkpoint
+    that an earlier run of the same job wrote with ``--checkpoint DIR``."""
+    if os.environ.get("PCL_METRICS", "0") == "1" or (pt is not None and pt.get("metrics", False)):
+        m.paracel_enable_metrics()
+    ck = os.environ.get("PCL_RESUME", "")
+    if ck:
+        from .utils import checkpoint as _ck
+        if _ck.exists(ck):
+            m.load_checkpoint(ck)
+    return m
+
+
+def _end(m):
+    ck = os.environ.get("PCL_CHECKPOINT", "")
+    if ck:
+        m.save_checkpoint(ck)
+    if m.timer is not None:
+        m.dump_phase_trace()
+    return m
+
+
 # ------------------------------------------------------------------ drivers
 def mf_gpu(comm, info, pt):
     from .models.mf_gpu import MfSgdGpu, balanced_groups, grid_rank
     dev = _device(comm)
     pattern = pt.check_parse("input", str)
-    first = next(iter(_partition(comm, pattern).load_lines(0, 1)), "")
+    first = next(iter(_partition(comm, pattern).load_blocks(0, 1)), "")
     drop = [2] if len(str_split(first, " \t")) >= 4 else []          # user item [date] rating
     uid, iid, val = _my_triples(comm, pattern, " \t", drop)
     unames, inames = _global_ids(comm, uid), _global_ids(comm, iid)
@@ -129,10 +152,14 @@ def mf_gpu(comm, info, pt):
     u, i, r = _exchange(comm, dev, dest, u, i, r)
     keep = _keep_last(u * len(inames) + i)
     m.load_ratings(u[keep], i[keep], r[keep])
-    m.solve()
+    m.init_parameters()
+    m.set_total_iters(m.rounds)
+    _begin(m, pt)                  # a checkpoint replaces the fresh parameters and sets the clock
+    m.paracel_sync()
+    m.fit()
     print("rmse:", m.rmse())
     m.dump_result()
-    return m
+    return _end(m)
 
 
 def pagerank_gpu(comm, info, pt):
@@ -152,9 +179,10 @@ def pagerank_gpu(comm, info, pt):
     # a repeated line is one edge: the reference keeps adj[v][w] (include/graph.hpp:226-232)
     keep = _keep_last(s * (SENTINEL + 1) + d)
     pr.load_edges(s[keep], d[keep])
-    pr.run(int(pt.get("rounds", 1)))
+    _begin(pr, pt)
+    pr.run(max(0, int(pt.get("rounds", 1)) - pr.it))
     pr.dump_result(pt.parse("output", str), names=names)
-    return pr
+    return _end(pr)
 
 
 def kmeans_gpu(comm, info, pt):
@@ -176,6 +204,7 @@ def kmeans_gpu(comm, info, pt):
     k = int(pt.get("kclusters", 2))
     km = KMeansGpu(k, X.shape[1], device=dev, comm=comm, output=pt.parse("output", str))
     km.load(X)                                   # the first k rows of worker 0 seed the centres
+    _begin(km, pt)
     km.fit(int(pt.get("rounds", 1)))
     C = km.cluster_centres()
     groups: Dict[int, List[str]] = {}
@@ -196,7 +225,7 @@ def kmeans_gpu(comm, info, pt):
                 f.write(f"{c}\t{'|'.join(merged[c])}\n")
         dump_dict_vector({c: C[c].cpu().tolist() for c in range(k)}, os.path.join(out, "centers_0"))
     km._barrier()
-    return km
+    return _end(km)
 
 
 def _linear_data(comm, pt, dev):
@@ -257,7 +286,9 @@ def l1_gpu(comm, info, pt, logistic: bool = True):
     """Sparse L1-regularised logistic regression (``lr_l1``) / Lasso by proximal gradient with the
     prox-L1 handler applied at the owners of the weight shards.  Input: the dense CSV of the
     serial tools (``f1,...,fk,label``; tool/lr_l1_serial.cpp:100-120) or sparse lines
-    ``label i:v i:v ...``.  Dumps ``lr_l1_weight_0`` / ``lasso_weight_0``."""
+    ``label i:v i:v ...``.  The objective is ``sum_i loss_i + lambda * |w|_1`` (``lambda`` weighs
+    the summed loss, as in the serial tools); ``eta`` is the step on the mean gradient.  Dumps
+    ``lr_l1_weight_0`` / ``lasso_weight_0``."""
     from .models.linear_gpu import SparseLinearGpu
     from .utils.dump import dump_vector
     dev = _device(comm)
@@ -325,6 +356,7 @@ def lda_gpu(comm, info, pt):
     m = LdaGibbsGpu(len(vocab), K, pt.get("alpha", None), float(pt.get("beta", 0.01)),
                     iters=int(pt.get("iters", 10)), nbatch=1, staleness=0, device=dev, comm=comm)
     m.load_docs(torch.as_tensor(ptr, device=dev), torch.as_tensor(words, device=dev))
+    _begin(m, pt)
     ll = m.fit(with_loglik=bool(pt.get("debug", False)))
     if ll:
         print("log-likelihood:", ll[-1], "perplexity:", m.perplexity(ll[-1]))
@@ -342,7 +374,7 @@ def lda_gpu(comm, info, pt):
                 best = np.argsort(-full[:, k], kind="stable")[:topk]
                 f.write(f"{k}topic\t" + "".join("%s:%f|" % (vocab[w], (full[w, k] + beta) / tot[k]) for w in best) + "\n")
     m._barrier()
-    return m
+    return _end(m)
 
 
 def als_gpu(comm, info, pt):

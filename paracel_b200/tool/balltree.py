@@ -90,6 +90,11 @@ class DeviceBalltree:
         self.ids = torch.as_tensor(order, device=dev)
         self.items = torch.as_tensor(tree.items[order].astype(np.float32), device=dev).contiguous()
         self.device = dev
+        # the search kernel follows these indices without checking them again (an unpickled tree
+        # could be damaged): child links are -1 or a node, item ranges lie inside the item array
+        from ..ops import _lib
+        _lib.validate_ids(self.child.view(-1), 0, self.radius.numel(), "ball tree (child links)", skip=-1)
+        _lib.validate_ids(self.range.view(-1), 0, self.n + 1, "ball tree (item ranges)")
 
     def search(self, queries, k: int = 1):
         """(indices [nq, k], scores [nq, k], balls opened [nq]) for a batch of queries; queries

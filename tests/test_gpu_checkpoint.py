@@ -33,7 +33,9 @@ def test_pagerank_resume_is_exact(tmp_path):
     c.load_checkpoint(str(tmp_path / "ck"))
     assert c.it == 3
     c.run(4)
-    assert torch.equal(c.ranks(), full)
+    # the edge-balanced kernel joins the partial sums of a row that spans blocks with atomics, whose
+    # order may differ between launches: equal to fp32 rounding, not necessarily bit for bit
+    torch.testing.assert_close(c.ranks(), full, rtol=2e-6, atol=1e-9)
     c.free()
 
 

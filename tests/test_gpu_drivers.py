@@ -158,7 +158,7 @@ def test_ridge_and_l1_drivers(monkeypatch, tmp_path):
     np.savetxt(inp, np.concatenate([X, y[:, None]], 1), delimiter=",", fmt="%.1f")
     out = tmp_path / "l1_out"
     _run(monkeypatch, tmp_path, "lr_l1", {"input": str(inp), "output": str(out) + "/", "rounds": 300,
-                                           "eta": 2.0, "lambda": 0.01})
+                                           "eta": 2.0, "lambda": 60.0})   # 0.01 per sample
     wv = np.asarray([float(x) for x in open(out / "lr_l1_weight_0").read().strip().split("|")])
     assert wv.shape == (d,)
     assert np.all(np.sign(wv[:4]) == np.sign(wt[:4])) and np.all(np.abs(wv[:4]) > 0.5)

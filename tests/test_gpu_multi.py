@@ -142,7 +142,9 @@ def test_launcher_gpu_switch_runs_pagerank_on_two_gpus(tmp_path):
         got[int(k)] = float(v)
     srcs = sorted({a for a, _ in edges})
     assert sorted(got) == srcs
-    # power iteration in plain Python
+    # power iteration in plain Python over the distinct edges: a repeated input line is one edge,
+    # as in the host path, whose graph container keeps adj[v][w]
+    edges = sorted(set(edges))
     nodes = sorted({a for a, _ in edges} | {b for _, b in edges})
     outdeg = {v: 0 for v in nodes}
     for a, _ in edges:

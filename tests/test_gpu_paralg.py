@@ -155,3 +155,23 @@ def test_device_models_are_paralg_subclasses():
     d = m.paracel_read_special("", "mf_H_filter")
     assert len(d) == 20 and d["H_3"] == m.Ht.shard[3].tolist()
     m.free()
+
+
+def test_clock_commit_is_withheld_after_a_failed_wait():
+    """A rank whose staleness wait ran out must not announce progress: the commit kernel looks
+    at the status block on the device and stores nothing while it holds an error."""
+    from paracel_b200.parallel.ssp_device import DeviceSspClock, SspTimeout
+    c = DeviceSspClock(1, 10, device="cuda:0")
+    c.commit()
+    torch.cuda.synchronize()
+    assert int(c.clocks[0]) == 1
+    c.status[0] = 1                    # what a timed-out wait leaves behind
+    c.commit()
+    torch.cuda.synchronize()
+    assert int(c.clocks[0]) == 1       # not announced
+    with pytest.raises(SspTimeout):
+        c.check()                      # reports and clears
+    c.commit()
+    torch.cuda.synchronize()
+    assert int(c.clocks[0]) == 3
+    c.free()
