@@ -123,24 +123,46 @@ __global__ void __launch_bounds__(256) dense_bupdate_kernel(BupArgs a) {
   const bool vec_ok = ((lo & 3) == 0);
   const long long nvec = vec_ok ? (n >> 2) : 0;
   float nz = 0.f;
-  for (long long v = tid; v < nvec; v += nth) {
-    const long long e = v << 2;
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 m = make_float4(-3.4e38f, -3.4e38f, -3.4e38f, -3.4e38f);
+  // four independent 16-byte columns per thread and trip: all their loads (the shard and every
+  // rank's delta) are issued before the first handler is applied
+  for (long long v0 = tid; v0 < nvec; v0 += 4 * nth) {
+    float4 s[4], m[4], t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long v = v0 + u * nth;
+      s[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      m[u] = make_float4(-3.4e38f, -3.4e38f, -3.4e38f, -3.4e38f);
+      if (v < nvec) t[u] = *reinterpret_cast<const float4*>(a.theta + (v << 2));
+    }
     for (int i = 0; i < a.world; ++i) {
       int r = a.rank + i;
       if (r >= a.world) r -= a.world;
-      const float4 d = pcl_ld_sys4(a.deltas[r] + lo + e);
-      s.x += d.x; s.y += d.y; s.z += d.z; s.w += d.w;
-      m.x = fmaxf(m.x, d.x); m.y = fmaxf(m.y, d.y); m.z = fmaxf(m.z, d.z); m.w = fmaxf(m.w, d.w);
+      float4 d[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long v = v0 + u * nth;
+        if (v < nvec) d[u] = pcl_ld_sys4(a.deltas[r] + lo + (v << 2));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (v0 + u * nth >= nvec) continue;
+        s[u].x += d[u].x; s[u].y += d[u].y; s[u].z += d[u].z; s[u].w += d[u].w;
+        m[u].x = fmaxf(m[u].x, d[u].x); m[u].y = fmaxf(m[u].y, d[u].y);
+        m[u].z = fmaxf(m[u].z, d[u].z); m[u].w = fmaxf(m[u].w, d[u].w);
+      }
     }
-    float4 t = *reinterpret_cast<float4*>(a.theta + e);
-    t.x = apply_handler(a.handler, t.x, s.x, m.x, a.lr, a.lambda);
-    t.y = apply_handler(a.handler, t.y, s.y, m.y, a.lr, a.lambda);
-    t.z = apply_handler(a.handler, t.z, s.z, m.z, a.lr, a.lambda);
-    t.w = apply_handler(a.handler, t.w, s.w, m.w, a.lr, a.lambda);
-    *reinterpret_cast<float4*>(a.theta + e) = t;
-    nz += (t.x != 0.f) + (t.y != 0.f) + (t.z != 0.f) + (t.w != 0.f);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long v = v0 + u * nth;
+      if (v >= nvec) continue;
+      float4 x = t[u];
+      x.x = apply_handler(a.handler, x.x, s[u].x, m[u].x, a.lr, a.lambda);
+      x.y = apply_handler(a.handler, x.y, s[u].y, m[u].y, a.lr, a.lambda);
+      x.z = apply_handler(a.handler, x.z, s[u].z, m[u].z, a.lr, a.lambda);
+      x.w = apply_handler(a.handler, x.w, s[u].w, m[u].w, a.lr, a.lambda);
+      *reinterpret_cast<float4*>(a.theta + (v << 2)) = x;
+      nz += (x.x != 0.f) + (x.y != 0.f) + (x.z != 0.f) + (x.w != 0.f);
+    }
   }
   for (long long e = (nvec << 2) + tid; e < n; e += nth) {
     float s = 0.f, m = -3.4e38f;

@@ -51,6 +51,30 @@ __device__ __forceinline__ Row8 load_cg(const float* row, int l) {
   return r;
 }
 
+// Packed pairs of fp32: sm_100 executes fma / mul / add on two fp32 values held in a 64-bit
+// register pair as ONE instruction (fma.rn.f32x2 ...).  The pass is bound by instruction issue, so
+// the element-wise parts of a rating (dot product, the two axpys, the fixed-point conversions'
+// scaling) are written on pairs: half the floating-point instructions for the same arithmetic.
+__device__ __forceinline__ unsigned long long pk2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void upk2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b,
+                                                   unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 constexpr float FX_SCALE = 4194304.f;          // 2^22
 constexpr float FX_INV = 1.f / 4194304.f;
 
@@ -61,10 +85,11 @@ __device__ __forceinline__ Row8 load_hot(const float* base_row, const int* delta
   const int4 d0 = *reinterpret_cast<const int4*>(delta_row + l * 4);
   const int4 d1 = *reinterpret_cast<const int4*>(delta_row + 64 + l * 4);
   Row8 r;
-  r.a.x = fmaf((float)d0.x, FX_INV, b0.x); r.a.y = fmaf((float)d0.y, FX_INV, b0.y);
-  r.a.z = fmaf((float)d0.z, FX_INV, b0.z); r.a.w = fmaf((float)d0.w, FX_INV, b0.w);
-  r.b.x = fmaf((float)d1.x, FX_INV, b1.x); r.b.y = fmaf((float)d1.y, FX_INV, b1.y);
-  r.b.z = fmaf((float)d1.z, FX_INV, b1.z); r.b.w = fmaf((float)d1.w, FX_INV, b1.w);
+  const unsigned long long inv2 = pk2(FX_INV, FX_INV);
+  upk2(fma2(pk2((float)d0.x, (float)d0.y), inv2, pk2(b0.x, b0.y)), r.a.x, r.a.y);
+  upk2(fma2(pk2((float)d0.z, (float)d0.w), inv2, pk2(b0.z, b0.w)), r.a.z, r.a.w);
+  upk2(fma2(pk2((float)d1.x, (float)d1.y), inv2, pk2(b1.x, b1.y)), r.b.x, r.b.y);
+  upk2(fma2(pk2((float)d1.z, (float)d1.w), inv2, pk2(b1.z, b1.w)), r.b.z, r.b.w);
   return r;
 }
 
@@ -77,28 +102,37 @@ __device__ __forceinline__ int to_fx(float x) { return __float2int_rn(x * FX_SCA
 
 __device__ __forceinline__ void add_hot(int* row, int l, const Row8& d) {
   int* p = row + l * 4;
-  atomicAdd(p, to_fx(d.a.x)); atomicAdd(p + 1, to_fx(d.a.y));
-  atomicAdd(p + 2, to_fx(d.a.z)); atomicAdd(p + 3, to_fx(d.a.w));
+  const unsigned long long sc2 = pk2(FX_SCALE, FX_SCALE);
+  float x0, x1, x2, x3, x4, x5, x6, x7;
+  upk2(mul2(pk2(d.a.x, d.a.y), sc2), x0, x1);
+  upk2(mul2(pk2(d.a.z, d.a.w), sc2), x2, x3);
+  upk2(mul2(pk2(d.b.x, d.b.y), sc2), x4, x5);
+  upk2(mul2(pk2(d.b.z, d.b.w), sc2), x6, x7);
+  atomicAdd(p, __float2int_rn(x0)); atomicAdd(p + 1, __float2int_rn(x1));
+  atomicAdd(p + 2, __float2int_rn(x2)); atomicAdd(p + 3, __float2int_rn(x3));
   p += 64;
-  atomicAdd(p, to_fx(d.b.x)); atomicAdd(p + 1, to_fx(d.b.y));
-  atomicAdd(p + 2, to_fx(d.b.z)); atomicAdd(p + 3, to_fx(d.b.w));
+  atomicAdd(p, __float2int_rn(x4)); atomicAdd(p + 1, __float2int_rn(x5));
+  atomicAdd(p + 2, __float2int_rn(x6)); atomicAdd(p + 3, __float2int_rn(x7));
 }
 
 __device__ __forceinline__ float dot8(const Row8& x, const Row8& y) {
-  float s = x.a.x * y.a.x;
-  s = fmaf(x.a.y, y.a.y, s); s = fmaf(x.a.z, y.a.z, s); s = fmaf(x.a.w, y.a.w, s);
-  s = fmaf(x.b.x, y.b.x, s); s = fmaf(x.b.y, y.b.y, s); s = fmaf(x.b.z, y.b.z, s);
-  s = fmaf(x.b.w, y.b.w, s);
-  return s;
+  unsigned long long s = mul2(pk2(x.a.x, x.a.y), pk2(y.a.x, y.a.y));
+  s = fma2(pk2(x.a.z, x.a.w), pk2(y.a.z, y.a.w), s);
+  s = fma2(pk2(x.b.x, x.b.y), pk2(y.b.x, y.b.y), s);
+  s = fma2(pk2(x.b.z, x.b.w), pk2(y.b.z, y.b.w), s);
+  float lo, hi;
+  upk2(s, lo, hi);
+  return lo + hi;
 }
 
 // out = p * x + q * y, element-wise
 __device__ __forceinline__ Row8 axpby(float p, const Row8& x, float q, const Row8& y) {
   Row8 o;
-  o.a.x = fmaf(p, x.a.x, q * y.a.x); o.a.y = fmaf(p, x.a.y, q * y.a.y);
-  o.a.z = fmaf(p, x.a.z, q * y.a.z); o.a.w = fmaf(p, x.a.w, q * y.a.w);
-  o.b.x = fmaf(p, x.b.x, q * y.b.x); o.b.y = fmaf(p, x.b.y, q * y.b.y);
-  o.b.z = fmaf(p, x.b.z, q * y.b.z); o.b.w = fmaf(p, x.b.w, q * y.b.w);
+  const unsigned long long p2 = pk2(p, p), q2 = pk2(q, q);
+  upk2(fma2(p2, pk2(x.a.x, x.a.y), mul2(q2, pk2(y.a.x, y.a.y))), o.a.x, o.a.y);
+  upk2(fma2(p2, pk2(x.a.z, x.a.w), mul2(q2, pk2(y.a.z, y.a.w))), o.a.z, o.a.w);
+  upk2(fma2(p2, pk2(x.b.x, x.b.y), mul2(q2, pk2(y.b.x, y.b.y))), o.b.x, o.b.y);
+  upk2(fma2(p2, pk2(x.b.z, x.b.w), mul2(q2, pk2(y.b.z, y.b.w))), o.b.z, o.b.w);
   return o;
 }
 
