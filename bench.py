@@ -286,7 +286,7 @@ def main():
                 "parallelism": "ps-shards-in-hbm x fsmap %dx%d" % (model.npx, model.npy),
                 "l2_policy": "inputs larger than L2 (126 MB): per rank %.0f MB of ratings are streamed and "
                              "%.0f MB of factor rows are read and updated every step"
-                             % (local_nnz * 4.4 / 1e6, factor_mb),
+                             % (local_nnz * (getattr(model, "packed_bits", 32) / 8 + 0.375) / 1e6, factor_mb),
                 "ratings_per_rank_max": int(mx.item()), "ratings_per_rank_min": int(mn.item()),
             },
             "clocks": clocks,

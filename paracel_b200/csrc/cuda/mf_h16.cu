@@ -38,6 +38,8 @@ struct MfH16Args {
   const int* chdr;
   const float* rtable;
   const float* hot_fs;   // per hot row: weight of a CTA's delta in the mix (null: flush_scale)
+  int packed_bits;       // 32: one word per rating (item | code << 24); 24: three bytes per rating
+                         // (item | code << 21), 24 words per chunk of 32 ratings
 };
 
 struct Row8 {
@@ -205,8 +207,31 @@ __global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
     float r0 = 0.f, r1 = 0.f;
     if (live) {
       if (a.packed != nullptr) {
-        const unsigned int pk0 = __ldg(a.packed + base + l);
-        const unsigned int pk1 = __ldg(a.packed + base + 16 + l);
+        unsigned int pk0, pk1;
+        if (a.packed_bits == 24) {
+          // 24 words per chunk: lane l of the half-warp holds words l and (l < 8) 16 + l; entry e
+          // starts at bit 24 e, i.e. in word (3 e) >> 2 at shift 8 * ((3 e) & 3)
+          const unsigned int* cw = a.packed + c * 24;
+          const unsigned int wa = __ldg(cw + l);
+          const unsigned int wb = l < 8 ? __ldg(cw + 16 + l) : 0u;
+          const int q0 = (3 * l) >> 2, q1 = (3 * (l + 16)) >> 2;          // q0 <= 11, 12 <= q1 <= 23
+          const int src_base = g << 4;
+          const unsigned int lo0 = __shfl_sync(gmask, wa, src_base + q0);
+          const unsigned int hi0 = __shfl_sync(gmask, wa, src_base + q0 + 1);   // q0 + 1 <= 12
+          const unsigned int a1 = __shfl_sync(gmask, wa, src_base + (q1 & 15));
+          const unsigned int b1 = __shfl_sync(gmask, wb, src_base + (q1 & 15));
+          const unsigned int a2 = __shfl_sync(gmask, wa, src_base + ((q1 + 1) & 15));
+          const unsigned int b2 = __shfl_sync(gmask, wb, src_base + ((q1 + 1) & 15));
+          const unsigned int lo1 = q1 < 16 ? a1 : b1;
+          const unsigned int hi1 = (q1 + 1) < 16 ? a2 : b2;   // word 24 (q1 = 23) is never needed: its lane reads 0
+          const unsigned int v0 = __funnelshift_r(lo0, hi0, 8 * ((3 * l) & 3)) & 0xffffffu;
+          const unsigned int v1 = __funnelshift_r(lo1, hi1, 8 * ((3 * (l + 16)) & 3)) & 0xffffffu;
+          pk0 = (v0 & 0x1fffffu) | ((v0 >> 21) << 24);
+          pk1 = (v1 & 0x1fffffu) | ((v1 >> 21) << 24);
+        } else {
+          pk0 = __ldg(a.packed + base + l);
+          pk1 = __ldg(a.packed + base + 16 + l);
+        }
         const int u_base = __ldg(a.chdr + 3 * c);
         const unsigned int inc = (unsigned int)__ldg(a.chdr + 3 * c + 1);
         const int n_valid = __ldg(a.chdr + 3 * c + 2);
@@ -326,14 +351,15 @@ __global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
 // Same contract as pcl_mf_sgd_pass (mf.cu) for D = 128: user-major sorted ratings in chunks of
 // 32, plain (ru, ri, rr) or compact (packed, chdr, rtable) stream, hot item rows (local index
 // below hot_T) replicated in shared memory and mixed every `cpw` chunks per half-warp with
-// weight `flush_scale` (<= 0: 1 / blocks) or, when `hot_fs` is given, with one weight per hot row.  `blocks` <= 0 selects one CTA per SM; `threads` is 512, 640 (default), 768 or 1024
+// weight `flush_scale` (<= 0: 1 / blocks) or, when `hot_fs` is given, with one weight per hot row.
+// `packed_bits` 24 selects the three-bytes-per-rating stream (21-bit item index, 3-bit rating code).  `blocks` <= 0 selects one CTA per SM; `threads` is 512, 640 (default), 768 or 1024
 // (threads / 16 chunks in flight per CTA).
 PCL_API int pcl_mf_sgd_pass_h16(const int* ru, const int* ri, const float* rr, long long nnz,
                                 float* W, float* H, float* bu, float* bi, const float* su,
                                 const float* si, float mu, float alpha, float beta, int hot_T,
                                 int cpw, float flush_scale, int blocks, double* sse,
                                 const unsigned int* packed, const int* chdr, const float* rtable,
-                                int threads, const float* hot_fs, cudaStream_t stream) {
+                                int threads, const float* hot_fs, int packed_bits, cudaStream_t stream) {
   if (nnz <= 0) return 0;
   if (nnz % 32 != 0 || hot_T < 0) return (int)cudaErrorInvalidValue;
   if (packed != nullptr && (chdr == nullptr || rtable == nullptr)) return (int)cudaErrorInvalidValue;
@@ -349,6 +375,8 @@ PCL_API int pcl_mf_sgd_pass_h16(const int* ru, const int* ri, const float* rr, l
   a.cpw = cpw > 0 ? cpw : 8;
   a.packed = packed; a.chdr = chdr; a.rtable = rtable;
   a.hot_fs = hot_fs;
+  if (packed != nullptr && packed_bits != 24 && packed_bits != 32) return (int)cudaErrorInvalidValue;
+  a.packed_bits = packed_bits;
   if (threads <= 0) threads = 640;   // 20 warps = 40 chunks in flight per CTA
   if (threads != 512 && threads != 640 && threads != 768 && threads != 1024) return (int)cudaErrorInvalidValue;
   if (blocks <= 0) blocks = 148;

@@ -159,6 +159,7 @@ class MfSgdGpu(paralg):
         # variant 2 (D = 128): experimental 8-lanes-per-rating kernel, 1 CTA per SM, 64 chunks
         self.variant = int(variant)
         self.compact = bool(compact)
+        self.allow_packed24 = os.environ.get("PCL_MF_PACKED24", "1") != "0"
         self.g8 = (self.D == 128 and self.variant == 2)
         # variant 3 (D = 128): sixteen lanes per rating, two chunks per warp, 1 CTA of 640 threads per SM
         self.h16 = (self.D == 128 and self.variant in (0, 3))
@@ -333,12 +334,14 @@ class MfSgdGpu(paralg):
         self._loaded = True
 
     def _build_compact(self, ru, ri, r):
-        """Compact rating stream (4 bytes per rating + 12 per chunk): item index and an 8-bit
-        rating code in one word; the users of a chunk as first index + increment mask (the users
-        of a user-major sorted chunk grow by 0 or 1 per rating).  Used when there are at most
-        2^24 local items and 256 distinct rating values."""
+        """Compact rating stream: per rating the item index and a rating code in 3 bytes (21 + 3
+        bits, when there are at most 2^21 local items and 8 distinct rating values) or in one
+        word (24 + 8 bits, up to 2^24 items and 256 values); per chunk of 32 ratings 12 bytes for
+        the users: first index + increment mask (the users of a user-major sorted chunk grow by
+        0 or 1 per rating).  3.375 or 4.375 bytes per rating instead of 12."""
         self.packed = self.chdr = self.rtable = None
         self.h_packed = self.h_chdr = None
+        self.packed_bits = 32
         if ru.numel() == 0:
             return
         vals = torch.unique(r)
@@ -349,7 +352,14 @@ class MfSgdGpu(paralg):
             return torch.where(x >= (1 << 31), x - (1 << 32), x).to(torch.int32)
         nch = ru.numel() // 32
         code = torch.searchsorted(vals, r).to(torch.int64)
-        self.packed = as_i32((code << 24) | ri.to(torch.int64)).contiguous()
+        if self.h16 and self.allow_packed24 and self.li.numel() <= (1 << 21) and vals.numel() <= 8:
+            # value e of a chunk occupies bits [24 e, 24 e + 24) of the chunk's 24 words
+            v = (code << 21) | ri.to(torch.int64)
+            b3 = torch.stack([v & 0xFF, (v >> 8) & 0xFF, (v >> 16) & 0xFF], dim=1).to(torch.uint8)
+            self.packed = b3.view(nch, 96).contiguous().view(torch.int32).reshape(-1).contiguous()
+            self.packed_bits = 24
+        else:
+            self.packed = as_i32((code << 24) | ri.to(torch.int64)).contiguous()
         u2 = ru.view(nch, 32).to(torch.int64)
         valid = u2 >= 0
         n_valid = valid.sum(1)
@@ -436,7 +446,7 @@ class MfSgdGpu(paralg):
                       self.bul, self.bil, self.su, self.si, self.mu, self.alpha, self.beta, self.hot_T,
                       self.chunks_per_flush, self.flush_scale, self.sgd_blocks, self.sse, pk,
                       self.chdr if pk is not None else None, self.rtable if pk is not None else None,
-                      self.h16_threads, self.hot_fs, s)
+                      self.h16_threads, self.hot_fs, self.packed_bits, s)
         elif self.h_ru is None:
             pk = self.packed if (self.compact and not self.g8) else None
             _lib.call("pcl_mf_sgd_pass", self.ru, self.ri, self.rr, self.ru.numel(), self.Wl,
@@ -461,7 +471,7 @@ class MfSgdGpu(paralg):
         if self.host_stream is None:
             self.host_stream = torch.cuda.Stream(device=dev)
             if compact:
-                self._stage = [(torch.empty(seg, dtype=torch.int32, device=dev),
+                self._stage = [(torch.empty(seg * self.packed_bits // 32, dtype=torch.int32, device=dev),
                                 torch.empty(3 * (seg // 32), dtype=torch.int32, device=dev)) for _ in range(2)]
             else:
                 self._stage = [(torch.empty(seg, dtype=torch.int32, device=dev),
@@ -481,10 +491,11 @@ class MfSgdGpu(paralg):
                     self.host_stream.wait_event(self._consumed[b])
                 if compact:
                     bpk, bhd = self._stage[b]
-                    bpk[:m].copy_(self.h_packed[off:off + m], non_blocking=True)
+                    w0, w1 = off * self.packed_bits // 32, (off + m) * self.packed_bits // 32
+                    bpk[: w1 - w0].copy_(self.h_packed[w0:w1], non_blocking=True)
                     c0, c1 = 3 * (off // 32), 3 * ((off + m) // 32)
                     bhd[: c1 - c0].copy_(self.h_chdr[c0:c1], non_blocking=True)
-                    nbytes = 4 * m + 4 * (c1 - c0)
+                    nbytes = 4 * (w1 - w0) + 4 * (c1 - c0)
                 else:
                     bru, bri, brr = self._stage[b]
                     bru[:m].copy_(self.h_ru[off:off + m], non_blocking=True)
@@ -515,7 +526,7 @@ class MfSgdGpu(paralg):
                 _lib.call("pcl_mf_sgd_pass_h16", seg_args[0], seg_args[1], seg_args[2], m, self.Wl, self.Hl,
                           self.bul, self.bil, self.su, self.si, self.mu, self.alpha, self.beta, self.hot_T,
                           self.chunks_per_flush, self.flush_scale, self.sgd_blocks, self.sse, seg_args[3], seg_args[4],
-                          seg_args[5], self.h16_threads, self.hot_fs, main.cuda_stream)
+                          seg_args[5], self.h16_threads, self.hot_fs, self.packed_bits, main.cuda_stream)
             else:
                 _lib.call("pcl_mf_sgd_pass", seg_args[0], seg_args[1], seg_args[2], m, self.Wl, self.Hl,
                           self.bul, self.bil, self.su, self.si, self.D, self.mu, self.alpha, self.beta,

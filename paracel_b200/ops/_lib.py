@@ -43,7 +43,7 @@ SIGS = {
     "pcl_rows_pull_i32": "ppiiqppqpip",
     "pcl_rows_push_i32": "ppiiqppiqpip",
     "pcl_mf_sgd_pass": "pppqppppppifffiifipipppp",
-    "pcl_mf_sgd_pass_h16": "pppqppppppfffiifippppipp",
+    "pcl_mf_sgd_pass_h16": "pppqppppppfffiifippppipip",
     "pcl_mf_sse": "pppqppppifppp",
     "pcl_gemm_tf32": "pppiiiqipppppiiiiipip",
     "pcl_gemm_tf32_2sm": "pppiiiqipppppiiiiipip",

@@ -211,7 +211,7 @@ def test_mf_streamed_rounds_equal_resident_rounds_statistically():
         m.fit()
         out.append(m.rmse())
         if host:
-            assert m.h2d_bytes == ((4 * 32 + 12) if compact else 12 * 32) * m.nchunks
+            assert m.h2d_bytes == ((m.packed_bits * 4 + 12) if compact else 12 * 32) * m.nchunks
         m.free()
     assert abs(out[0] - out[1]) < 0.02 * out[0] and abs(out[0] - out[2]) < 0.02 * out[0], out
 

@@ -175,3 +175,35 @@ def test_clock_commit_is_withheld_after_a_failed_wait():
     torch.cuda.synchronize()
     assert int(c.clocks[0]) == 3
     c.free()
+
+
+def test_ssp_cache_rule_on_device_reads():
+    """Under SSP a copy pulled at clock c is served while clock - c < limit_s (no kernel runs),
+    the first read and the reads after the last iteration always pull."""
+    from paracel_b200.ops import _lib
+    from paracel_b200.paralg import paralg
+    pt = paralg(None, rounds=6, limit_s=2, ssp_switch=True, backend="gpu", device="cuda:0")
+    try:
+        T = pt.paracel_row_table(64, 8, prefix="R_")
+        pt.paracel_dense_table("theta", 40)
+        kb = pt.paracel_keys(T, torch.arange(0, 64, 3, device="cuda"))
+        out = torch.empty(len(kb), 8, device="cuda")
+        pulls = []
+        for it in range(6):
+            n0 = _lib.launches()
+            pt.paracel_read_multi(kb, out=out)
+            pt.paracel_read("theta")
+            pulls.append(_lib.launches() - n0)
+            pt.paracel_bupdate_multi(kb, torch.ones(len(kb), 8, device="cuda"), "", "add")
+            pt.iter_commit()
+        # clock 0: pull; 1: cached; 2: pull (2 clocks old); 3: cached; 4: pull; 5: cached
+        assert [p > 0 for p in pulls] == [True, False, True, False, True, False]
+        n0 = _lib.launches()
+        pt.paracel_read_multi(kb, out=out)            # clock == total_iters: always pulls
+        assert _lib.launches() > n0
+        torch.cuda.synchronize()
+        assert float(out[0, 0]) == 6.0                 # six pushes of one arrived at the owner
+        assert pt.paracel_would_pull(kb, out)
+        pt.paracel_check()
+    finally:
+        pt.close()
