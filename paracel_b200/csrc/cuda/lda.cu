@@ -18,6 +18,9 @@
 // sampled (software pipelining of the L2 latency).  The second row costs 32 more registers
 // (162 instead of 128 at K = 1024), residency drops from 16 to 12 warps per SM and the
 // sampler went from 1.33 G to 0.84 G tokens/s on the 1 M-document configuration.
+// Kept: 1 / (n_k + V beta) in shared memory instead of registers (128 -> 95 registers, 16 -> 20
+// warps per SM, 1.32 G -> 1.41 G tokens/s).  Parking the lane's running sums there as well (80
+// registers, 24 warps, 32 KB of shared memory per block) was slower again: 1.36 G.
 #include "common.cuh"
 
 namespace {
@@ -46,24 +49,27 @@ template <int J>
 __global__ void __launch_bounds__(128) lda_gibbs_kernel(LdaArgs a) {
   constexpr int K = 128 * J;
   constexpr int R = 4 * J;  // topics per lane
+  // 1 / (n_k + V beta) of the lane's topics lives in shared memory, not in registers: the lane
+  // writes its R values at the start of a document and reads them back (J 128-bit loads) for every
+  // token.  At K = 1024 this takes the kernel from 128 to about 96 registers, i.e. from 16 to 20
+  // resident warps per SM, which matters because the sampler is bound by latency.
+  __shared__ float4 s_inv[4][J][32];
   const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long d = warp; d < a.n_docs; d += nwarps) {
     const long long t0 = a.doc_ptr[d], t1 = a.doc_ptr[d + 1];
     if (t1 <= t0) continue;
     int nd[R];
-    float inv[R];
     int* ndp = a.n_dk + d * K;
 #pragma unroll
     for (int j = 0; j < J; ++j) {
       const int4 v = *reinterpret_cast<const int4*>(ndp + 128 * j + 4 * lane);
       nd[4 * j] = v.x; nd[4 * j + 1] = v.y; nd[4 * j + 2] = v.z; nd[4 * j + 3] = v.w;
       const int4 s = __ldcg(reinterpret_cast<const int4*>(a.n_k + 128 * j + 4 * lane));
-      inv[4 * j] = 1.f / ((float)s.x + a.vbeta);
-      inv[4 * j + 1] = 1.f / ((float)s.y + a.vbeta);
-      inv[4 * j + 2] = 1.f / ((float)s.z + a.vbeta);
-      inv[4 * j + 3] = 1.f / ((float)s.w + a.vbeta);
+      s_inv[wib][j][lane] = make_float4(1.f / ((float)s.x + a.vbeta), 1.f / ((float)s.y + a.vbeta),
+                                        1.f / ((float)s.z + a.vbeta), 1.f / ((float)s.w + a.vbeta));
     }
     for (long long t = t0; t < t1; ++t) {
       const int w = __ldg(a.words + t);
@@ -86,12 +92,14 @@ __global__ void __launch_bounds__(128) lda_gibbs_kernel(LdaArgs a) {
       for (int j = 0; j < J; ++j) {
         const int4 v = __ldcg(reinterpret_cast<const int4*>(nwp + 128 * j + 4 * lane));
         const int c[4] = {v.x, v.y, v.z, v.w};
+        const float4 iv4 = s_inv[wib][j][lane];
+        const float iv[4] = {iv4.x, iv4.y, iv4.z, iv4.w};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int r = 4 * j + q;
           // a concurrent document may have pushed a count of this word below zero transiently
           const float nw = fmaxf((float)c[q], 0.f);
-          run += ((float)nd[r] + a.alpha) * (nw + a.beta) * inv[r];
+          run += ((float)nd[r] + a.alpha) * (nw + a.beta) * iv[q];
           p[r] = run;
         }
       }
@@ -172,16 +180,27 @@ PCL_API int pcl_lda_gibbs(const long long* doc_ptr, const int* words, int* z, in
                           unsigned long long seed, int blocks, cudaStream_t stream) {
   if (n_docs <= 0) return 0;
   LdaArgs a{doc_ptr, words, z, n_dk, n_wk, n_k, n_docs, alpha, beta, vbeta, seed};
-  if (blocks <= 0) blocks = 148 * 4;
-  long long need = (n_docs + 3) / 4;
-  if (need < blocks) blocks = (int)need;
+  // default grid: as many blocks as fit on the device at once (the warps loop over the documents)
+#define PCL_LDA_LAUNCH(JJ)                                                                          \
+  {                                                                                                 \
+    if (blocks <= 0) {                                                                              \
+      int per_sm = 0;                                                                               \
+      cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lda_gibbs_kernel<JJ>, 128, 0); \
+      if (e != cudaSuccess) return (int)e;                                                          \
+      blocks = 148 * (per_sm > 0 ? per_sm : 4);                                                     \
+    }                                                                                               \
+    const long long need = (n_docs + 3) / 4;                                                        \
+    if (need < blocks) blocks = (int)need;                                                          \
+    lda_gibbs_kernel<JJ><<<blocks, 128, 0, stream>>>(a);                                            \
+  }
   switch (K) {
-    case 128: lda_gibbs_kernel<1><<<blocks, 128, 0, stream>>>(a); break;
-    case 256: lda_gibbs_kernel<2><<<blocks, 128, 0, stream>>>(a); break;
-    case 512: lda_gibbs_kernel<4><<<blocks, 128, 0, stream>>>(a); break;
-    case 1024: lda_gibbs_kernel<8><<<blocks, 128, 0, stream>>>(a); break;
+    case 128: PCL_LDA_LAUNCH(1) break;
+    case 256: PCL_LDA_LAUNCH(2) break;
+    case 512: PCL_LDA_LAUNCH(4) break;
+    case 1024: PCL_LDA_LAUNCH(8) break;
     default: return (int)cudaErrorInvalidValue;
   }
+#undef PCL_LDA_LAUNCH
   return pcl_last_error();
 }
 

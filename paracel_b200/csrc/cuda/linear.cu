@@ -254,14 +254,21 @@ PCL_API int pcl_lr_sparse_grad(const long long* row_ptr, const int* cols, const 
                                int hot_T, float* g, double* loss, int blocks, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (hot_T < 0 || hot_T > 24 * 1024) return (int)cudaErrorInvalidValue;
-  if (blocks <= 0) blocks = 148 * 4;
-  long long need = (n + 7) / 8;
-  if (need < blocks) blocks = (int)need;
   SparseGradArgs a{row_ptr, cols, vals, y, theta, n, logistic, hot_T, g, loss};
   size_t smem = (size_t)hot_T * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(sparse_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return (int)e;
+  if (blocks <= 0) {
+    // as many blocks as are resident at once (the kernel is bound by gather / atomic latency,
+    // so every resident warp counts; the shared-memory table of hot features sets the limit)
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sparse_grad_kernel, 256, smem);
+    if (e != cudaSuccess) return (int)e;
+    blocks = 148 * (per_sm > 0 ? per_sm : 4);
+  }
+  long long need = (n + 7) / 8;
+  if (need < blocks) blocks = (int)need;
   sparse_grad_kernel<<<blocks, 256, smem, stream>>>(a);
   return pcl_last_error();
 }

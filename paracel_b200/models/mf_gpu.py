@@ -313,10 +313,7 @@ class MfSgdGpu(paralg):
             self.h_ri = ri.cpu().pin_memory()
             self.h_rr = r.cpu().pin_memory()
             self.ru = self.ri = self.rr = None
-            if self.packed is not None:
-                self.h_packed = self.packed.cpu().pin_memory()
-                self.h_chdr = self.chdr.cpu().pin_memory()
-                self.packed = self.chdr = None
+            self._offload_compact()
         else:
             self.ru, self.ri, self.rr = ru, ri, r
             self.h_ru = None
@@ -341,7 +338,11 @@ class MfSgdGpu(paralg):
         0 or 1 per rating).  3.375 or 4.375 bytes per rating instead of 12."""
         self.packed = self.chdr = self.rtable = None
         self.h_packed = self.h_chdr = None
-        self.packed_bits = 32
+        # The one-word form feeds the kernel when the ratings are resident in HBM (its decode is
+        # a mask and a shift); the three-byte form is what is streamed from host memory in
+        # out-of-core mode, where the bytes of the copy set the pace.
+        self.packed24 = None
+        self.packed_bits = 32          # form of the stream that the host copy holds
         if ru.numel() == 0:
             return
         vals = torch.unique(r)
@@ -352,14 +353,12 @@ class MfSgdGpu(paralg):
             return torch.where(x >= (1 << 31), x - (1 << 32), x).to(torch.int32)
         nch = ru.numel() // 32
         code = torch.searchsorted(vals, r).to(torch.int64)
+        self.packed = as_i32((code << 24) | ri.to(torch.int64)).contiguous()
         if self.h16 and self.allow_packed24 and self.li.numel() <= (1 << 21) and vals.numel() <= 8:
             # value e of a chunk occupies bits [24 e, 24 e + 24) of the chunk's 24 words
             v = (code << 21) | ri.to(torch.int64)
             b3 = torch.stack([v & 0xFF, (v >> 8) & 0xFF, (v >> 16) & 0xFF], dim=1).to(torch.uint8)
-            self.packed = b3.view(nch, 96).contiguous().view(torch.int32).reshape(-1).contiguous()
-            self.packed_bits = 24
-        else:
-            self.packed = as_i32((code << 24) | ri.to(torch.int64)).contiguous()
+            self.packed24 = b3.view(nch, 96).contiguous().view(torch.int32).reshape(-1).contiguous()
         u2 = ru.view(nch, 32).to(torch.int64)
         valid = u2 >= 0
         n_valid = valid.sum(1)
@@ -381,10 +380,16 @@ class MfSgdGpu(paralg):
         self.h_ri = self.ri.cpu().pin_memory()
         self.h_rr = self.rr.cpu().pin_memory()
         self.ru = self.ri = self.rr = None
-        if self.packed is not None:
-            self.h_packed = self.packed.cpu().pin_memory()
-            self.h_chdr = self.chdr.cpu().pin_memory()
-            self.packed = self.chdr = None
+        self._offload_compact()
+
+    def _offload_compact(self):
+        if self.packed is None:
+            return
+        src = self.packed24 if self.packed24 is not None else self.packed
+        self.packed_bits = 24 if self.packed24 is not None else 32
+        self.h_packed = src.cpu().pin_memory()
+        self.h_chdr = self.chdr.cpu().pin_memory()
+        self.packed = self.packed24 = self.chdr = None
 
     # ------------------------------------------------------------ parameters
     def init_parameters(self):
@@ -446,7 +451,7 @@ class MfSgdGpu(paralg):
                       self.bul, self.bil, self.su, self.si, self.mu, self.alpha, self.beta, self.hot_T,
                       self.chunks_per_flush, self.flush_scale, self.sgd_blocks, self.sse, pk,
                       self.chdr if pk is not None else None, self.rtable if pk is not None else None,
-                      self.h16_threads, self.hot_fs, self.packed_bits, s)
+                      self.h16_threads, self.hot_fs, 32, s)
         elif self.h_ru is None:
             pk = self.packed if (self.compact and not self.g8) else None
             _lib.call("pcl_mf_sgd_pass", self.ru, self.ri, self.rr, self.ru.numel(), self.Wl,

@@ -121,19 +121,24 @@ def test_mf_single_chunk_matches_sequential_oracle():
     from paracel_b200.models.mf_gpu import MfSgdGpu
     dev = "cuda:0"
     g = torch.Generator().manual_seed(3)
-    for k, hot, variant, compact in ((32, 64, 0, True), (80, 64, 0, False), (128, 64, 1, True),
-                                     (128, 0, 1, False), (64, 3, 0, True), (128, 64, 2, True),
-                                     (100, 0, 2, True), (128, 4, 2, True), (128, 64, 3, True),
-                                     (128, 0, 3, False), (100, 4, 3, True), (128, 5, 3, False)):
+    # host: ratings streamed from pinned host memory (at rank 128 in the three-byte form)
+    for k, hot, variant, compact, host in (
+            (32, 64, 0, True, False), (80, 64, 0, False, False), (128, 64, 1, True, False),
+            (128, 0, 1, False, False), (64, 3, 0, True, False), (128, 64, 2, True, False),
+            (100, 0, 2, True, False), (128, 4, 2, True, False), (128, 64, 3, True, False),
+            (128, 0, 3, False, False), (100, 4, 3, True, False), (128, 5, 3, False, False),
+            (128, 64, 0, True, True), (128, 0, 3, True, True), (100, 4, 0, True, True)):
         nu, ni, nnz = 6, 9, 31
         u = torch.randint(0, nu, (nnz,), generator=g)
         i = torch.randint(0, ni, (nnz,), generator=g)
         r = torch.randint(1, 6, (nnz,), generator=g).float()
         m = MfSgdGpu(nu, ni, k=k, alpha=0.05, beta=0.02, rounds=1, device=dev, hot_rows=hot,
                      variant=variant, compact=compact)
-        m.load_ratings(u, i, r)
+        m.load_ratings(u, i, r, keep_on_host=host)
         m.init_parameters()
         assert torch.all(m.su == 1) and torch.all(m.si == 1)
+        if host:
+            assert m.packed_bits == 24 and m.h_packed.numel() == 24 * m.nchunks
         W0 = m.Wt.shard[:nu, :k].cpu()
         H0 = m.Ht.shard[:ni, :k].cpu()
         bu0, bi0 = m.but.shard[:nu].cpu(), m.bit.shard[:ni].cpu()
