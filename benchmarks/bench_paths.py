@@ -34,6 +34,8 @@ def main():
     ap.add_argument("--push-rows", type=int, default=0, help="rows path: rows pulled / pushed per rank")
     ap.add_argument("--sorted-ids", action="store_true", help="rows path: ascending ids instead of a random order")
     ap.add_argument("--kernel", default=None, choices=["1sm", "2sm"], help="GEMM kernel of gather_gemm")
+    ap.add_argument("--gather-ctas", type=int, default=0, help="gather_gemm: CTAs that stage the peers' shards "
+                    "(0: the operator's default)")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -142,7 +144,7 @@ def main():
     elif args.path == "gather_gemm":
         from paracel_b200.ops.gemm import DenseReadGemm
         N, K, M = (4096, 256, 32768) if args.small else (16384, 512, 65536)
-        op = DenseReadGemm(N, K, kernel=args.kernel)
+        op = DenseReadGemm(N, K, kernel=args.kernel, **({"gather_ctas": args.gather_ctas} if args.gather_ctas else {}))
         op.shard.normal_()
         A = torch.randn(M, K, device=dev)
         C = torch.empty(M, N, device=dev)
@@ -153,7 +155,7 @@ def main():
         gathered = (world - 1) / world * N * K * 4
         t_flops = flops / (peaks.get("bf16_tflops", 1590.0) / 2 * 1e12) * 1e3   # tf32 = half the bf16 rate
         t_link = gathered / (NVLINK_GBS * 1e9) * 1e3
-        out.update({"kernel": args.kernel or "default", "M": M, "N": N, "K": K, "ms": ms, "tflops": flops / ms / 1e9,
+        out.update({"kernel": args.kernel or "default", "gather_ctas": op.gather_ctas, "M": M, "N": N, "K": K, "ms": ms, "tflops": flops / ms / 1e9,
                     "gathered_MB": gathered / 1e6, "roofline_ms": max(t_flops, t_link),
                     "frac_of_roofline": max(t_flops, t_link) / ms,
                     "roofline_note": "max(FLOPs / (measured bf16 burst / 2), gathered bytes / 770 GB/s)"})

@@ -245,42 +245,100 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   if (a.world > 1) first_local = (int)(((long long)a.rank * a.rows_per_shard) / TN) % n_tiles;
 
   // ------------------------------------------------- gather CTAs (whole clusters)
+  // One thread per gather CTA drives the copy engine of its SM: contiguous pieces of a peer's
+  // shard (up to 32 KB) are fetched into shared memory with cp.async.bulk (a plain bulk load, no
+  // multicast; the source is the peer's memory over NVLink), and each piece that has landed goes
+  // on to the local staging buffer with a bulk store.  GBUF pieces are in flight per CTA, which
+  // is what the NVLink latency needs: with 128-bit loads issued by the CTA's threads a CTA moved
+  // about 20 GB/s and sixteen CTAs had to be taken from the tensor cores.
   if ((int)blockIdx.x < a.gather_ctas) {
-    const int kv = a.K >> 2;
-    for (int ord = blockIdx.x; ord < n_tiles; ord += a.gather_ctas) {
-      const int nt = tile_at(ord, n_tiles, first_local);
-      const int r0 = nt * TN;
-      const int r1 = min(a.N, r0 + TN);
-      // eight 128-bit peer loads in flight per thread before the first store
-      const long long total = (long long)(r1 - r0) * kv;
-      for (long long base = threadIdx.x; base < total; base += (long long)blockDim.x * 8) {
-        float4 v[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const long long idx = base + (long long)u * blockDim.x;
-          if (idx < total) {
-            const int row = r0 + (int)(idx / kv);
-            const int c = (int)(idx % kv);
-            const int owner = min(row / a.rows_per_shard, a.world - 1);
-            v[u] = pcl_ld_sys4(a.b_shards[owner] + (long long)(row - owner * a.rows_per_shard) * a.K + 4 * c);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const long long idx = base + (long long)u * blockDim.x;
-          if (idx < total) {
-            const int row = r0 + (int)(idx / kv);
-            const int c = (int)(idx % kv);
-            *reinterpret_cast<float4*>(a.b_stage + (long long)row * a.K + 4 * c) = v[u];
-          }
-        }
-      }
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        __threadfence();
-        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(a.flags + nt), "r"(a.epoch) : "memory");
-      }
+    constexpr int GBUF = 6;
+    constexpr uint32_t GCH = 32768;
+    uint8_t* gbase = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* gbar = (uint64_t*)(gbase + GBUF * GCH);
+    __shared__ int g_abort;
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < GBUF; ++i) mbar_init(gbar + i, 1);
+      g_abort = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    const long long row_bytes = (long long)a.K * 4;
+    // the pieces of this CTA's tiles form one sequence; piece q uses buffer q % GBUF
+    struct Piece { const uint8_t* src; uint8_t* dst; uint32_t bytes; int tile_end; };
+    auto piece_at = [&](int ord, long long off_in_tile, Piece& pc) -> bool {
+      // tile `ord` of this CTA's list; off_in_tile counts bytes from the tile's first row
+      const int nt = tile_at(ord, n_tiles, first_local);
+      const long long r0 = (long long)nt * TN;
+      const long long r1 = min((long long)a.N, r0 + TN);
+      const long long tile_bytes = (r1 - r0) * row_bytes;
+      if (off_in_tile >= tile_bytes) return false;
+      const long long row = r0 + off_in_tile / row_bytes;
+      const int owner = (int)min(row / a.rows_per_shard, (long long)a.world - 1);
+      const long long owner_end_row = min(r1, (long long)(owner + 1) * a.rows_per_shard +
+                                                  (owner == a.world - 1 ? (long long)a.N : 0));
+      const long long seg_end = (owner_end_row - r0) * row_bytes;     // end of this owner's part of the tile
+      long long n = seg_end - off_in_tile;
+      if (n > GCH) n = GCH;
+      pc.src = reinterpret_cast<const uint8_t*>(a.b_shards[owner]) +
+               (row - (long long)owner * a.rows_per_shard) * row_bytes + off_in_tile % row_bytes;
+      pc.dst = reinterpret_cast<uint8_t*>(a.b_stage) + r0 * row_bytes + off_in_tile;
+      pc.bytes = (uint32_t)n;
+      pc.tile_end = (off_in_tile + n >= tile_bytes) ? nt : -1;
+      return true;
+    };
+    // two cursors over the same piece sequence: `ld` issues loads GBUF pieces ahead of `st`
+    int ld_ord = blockIdx.x, st_ord = blockIdx.x;
+    long long ld_off = 0, st_off = 0;
+    long long issued = 0, stored = 0;
+    bool ok = true;
+    auto issue_load = [&]() {
+      Piece pc;
+      while (ld_ord < n_tiles && !piece_at(ld_ord, ld_off, pc)) { ld_ord += a.gather_ctas; ld_off = 0; }
+      if (ld_ord >= n_tiles) return false;
+      const int bidx = (int)(issued % GBUF);
+      mbar_expect_tx(gbar + bidx, pc.bytes);
+      asm volatile(
+          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+          ::"r"(smem_u32(gbase + bidx * GCH)), "l"(pc.src), "r"(pc.bytes), "r"(smem_u32(gbar + bidx))
+          : "memory");
+      ld_off += pc.bytes;
+      ++issued;
+      return true;
+    };
+    for (int i = 0; i < GBUF; ++i)
+      if (!issue_load()) break;
+    while (stored < issued && ok) {
+      Piece pc;
+      while (!piece_at(st_ord, st_off, pc)) { st_ord += a.gather_ctas; st_off = 0; }
+      const int bidx = (int)(stored % GBUF);
+      if (!mbar_wait(gbar + bidx, (uint32_t)((stored / GBUF) & 1), &g_abort)) {
+        report(a.status, a.rank, 35, stored, bidx);
+        ok = false;
+        break;
+      }
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(pc.dst),
+                   "r"(smem_u32(gbase + bidx * GCH)), "r"(pc.bytes)
+                   : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      st_off += pc.bytes;
+      ++stored;
+      if (pc.tile_end >= 0) {
+        // the tile is complete once every store so far has been written
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        __threadfence();
+        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(a.flags + pc.tile_end), "r"(a.epoch) : "memory");
+      } else {
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the buffer may be refilled
+      }
+      issue_load();
+    }
+    if (!ok) {
+      // give the loads that are still in flight time to land before the shared memory goes away
+      for (int s_ = 0; s_ < 2048; ++s_) __nanosleep(1000);
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     return;
   }
 

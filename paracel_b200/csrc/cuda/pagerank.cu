@@ -112,7 +112,22 @@ __global__ void __launch_bounds__(256) pagerank_stream_kernel(const long long* r
     const long long nrows = r1 - r0 + 1;
     __syncthreads();
     if (threadIdx.x == 0) n_long = 0;
-    for (long long p = s + threadIdx.x; p < e; p += blockDim.x) sv[p - s] = __ldg(contrib + cols[p]);
+    // all index loads of the thread first, then all gathers, then the stores: eight independent
+    // random reads in flight per thread instead of a load-use chain per element
+    {
+      int ci[PR_CAP / 256];
+      float cv[PR_CAP / 256];
+#pragma unroll
+      for (int q = 0; q < PR_CAP / 256; ++q) {
+        const long long p = s + threadIdx.x + q * 256;
+        ci[q] = p < e ? __ldg(cols + p) : -1;
+      }
+#pragma unroll
+      for (int q = 0; q < PR_CAP / 256; ++q) cv[q] = ci[q] >= 0 ? __ldg(contrib + ci[q]) : 0.f;
+#pragma unroll
+      for (int q = 0; q < PR_CAP / 256; ++q)
+        if (ci[q] >= 0) sv[threadIdx.x + q * 256] = cv[q];
+    }
     const bool cached = nrows <= PR_ROWS;
     if (cached) {
       for (int i = threadIdx.x; i <= (int)nrows; i += blockDim.x) {

@@ -139,7 +139,7 @@ class DenseReadGemm:
     make sure nobody writes the shards while a call is in flight (barrier or SSP clock).
     """
 
-    def __init__(self, N: int, K: int, group=None, device=None, gather_ctas: int = 16,
+    def __init__(self, N: int, K: int, group=None, device=None, gather_ctas: int = 8,
                  kernel: Optional[str] = None):
         if K % 4:
             raise ValueError("K must be a multiple of 4")
