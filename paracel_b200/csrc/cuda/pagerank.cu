@@ -90,11 +90,14 @@ __global__ void __launch_bounds__(256) pagerank_heavy_kernel(PrArgs a) {
 // longer than a block) is accumulated with atomicAdd, so `acc` must be zero on entry.  The
 // damping epilogue is a second, element-wise kernel because a cut row is only complete once
 // all its blocks have run.
-constexpr int PR_CAP = 2048;
+// PR_CAP is 2048 or 4096 in-links per block (template parameter).  Which is faster depends on the
+// graph's labelling (R-MAT 26, one GPU: raw labels 6.28 ms with 2048 and 6.04 ms with 4096;
+// block-scrambled labels 7.74 ms and 8.97 ms), so the model times both once at load time.
 constexpr int PR_ROWS = 1024;   // row pointers of a block cached in shared memory up to this many rows
 
 // blk_first[b] / blk_last[b]: the rows that contain in-link b * PR_CAP and the last in-link of
 // block b (static per graph, computed once at load time).
+template <int PR_CAP>
 __global__ void __launch_bounds__(256) pagerank_stream_kernel(const long long* row_ptr, const int* cols,
                                                               const float* contrib,
                                                               const int* blk_first, const int* blk_last,
@@ -114,19 +117,20 @@ __global__ void __launch_bounds__(256) pagerank_stream_kernel(const long long* r
     if (threadIdx.x == 0) n_long = 0;
     // all index loads of the thread first, then all gathers, then the stores: eight independent
     // random reads in flight per thread instead of a load-use chain per element
-    {
-      int ci[PR_CAP / 256];
-      float cv[PR_CAP / 256];
 #pragma unroll
-      for (int q = 0; q < PR_CAP / 256; ++q) {
-        const long long p = s + threadIdx.x + q * 256;
+    for (int h = 0; h < PR_CAP / 2048; ++h) {   // batches of eight gathers per thread
+      int ci[8];
+      float cv[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const long long p = s + threadIdx.x + (h * 8 + q) * 256;
         ci[q] = p < e ? __ldg(cols + p) : -1;
       }
 #pragma unroll
-      for (int q = 0; q < PR_CAP / 256; ++q) cv[q] = ci[q] >= 0 ? __ldg(contrib + ci[q]) : 0.f;
+      for (int q = 0; q < 8; ++q) cv[q] = ci[q] >= 0 ? __ldg(contrib + ci[q]) : 0.f;
 #pragma unroll
-      for (int q = 0; q < PR_CAP / 256; ++q)
-        if (ci[q] >= 0) sv[threadIdx.x + q * 256] = cv[q];
+      for (int q = 0; q < 8; ++q)
+        if (ci[q] >= 0) sv[threadIdx.x + (h * 8 + q) * 256] = cv[q];
     }
     const bool cached = nrows <= PR_ROWS;
     if (cached) {
@@ -197,19 +201,23 @@ __global__ void __launch_bounds__(256) pagerank_epilogue_kernel(PrArgs a, const 
 }  // namespace
 
 // Edge-balanced pull step.  `acc` is a scratch vector of n_local floats; it is cleared here.
-// blk_first / blk_last have ceil(nnz / 2048) entries (see pagerank_stream_kernel).
+// blk_first / blk_last have ceil(nnz / cap) entries (see pagerank_stream_kernel); cap is 2048 or 4096.
 PCL_API int pcl_pagerank_pull_stream(const long long* row_ptr, const int* cols, const float* contrib,
                                      const float* inv_outdeg, long long n_local, long long nnz,
                                      const int* blk_first, const int* blk_last, float damping, float* acc, float* new_contrib, float* new_rank,
-                                     double* delta_l1, const float* old_rank, cudaStream_t stream) {
+                                     double* delta_l1, const float* old_rank, int cap, cudaStream_t stream) {
   if (n_local <= 0) return 0;
+  if (cap != 2048 && cap != 4096) return (int)cudaErrorInvalidValue;
   if (delta_l1 != nullptr && (old_rank == nullptr || new_rank == nullptr)) return (int)cudaErrorInvalidValue;
   cudaError_t e = cudaMemsetAsync(acc, 0, (size_t)n_local * sizeof(float), stream);
   if (e != cudaSuccess) return (int)e;
   if (nnz > 0) {
-    long long blocks = (nnz + PR_CAP - 1) / PR_CAP;
+    long long blocks = (nnz + cap - 1) / cap;
     if (blocks > 148LL * 64) blocks = 148LL * 64;
-    pagerank_stream_kernel<<<(int)blocks, 256, 0, stream>>>(row_ptr, cols, contrib, blk_first, blk_last, nnz, acc);
+    if (cap == 2048)
+      pagerank_stream_kernel<2048><<<(int)blocks, 256, 0, stream>>>(row_ptr, cols, contrib, blk_first, blk_last, nnz, acc);
+    else
+      pagerank_stream_kernel<4096><<<(int)blocks, 256, 0, stream>>>(row_ptr, cols, contrib, blk_first, blk_last, nnz, acc);
   }
   PrArgs a{row_ptr, cols, contrib, inv_outdeg, n_local, damping, new_contrib, new_rank, delta_l1,
            old_rank, 0, nullptr, 0};

@@ -83,13 +83,38 @@ class PageRankGpu(paralg):
         self.rank_local = torch.where(self.has_out, torch.full_like(od, init), torch.zeros_like(od))
         self.rank_new = torch.empty_like(self.rank_local)
         self.acc = torch.zeros(max(self.n_local, 1), device=dev)
-        self.plan = pagerank_stream_plan(self.row_ptr)
+        self.plan = self._choose_plan()
         # contribution table for iteration 0 lives in tables[0]
         for k in self.KEYS:
             self.paracel_local_shard(k).zero_()
         self.paracel_local_shard(k0)[: self.n_local] = self.rank_local * self.inv_outdeg
         self.paracel_commit_write(k0)
         self.it = 0
+
+    def _choose_plan(self):
+        """Edge-balanced kernel with 2048 or 4096 in-links per block: whichever is faster on this
+        graph (the labelling decides; one timed launch each on scratch outputs).  All ranks take
+        the choice of the slowest rank's best, so the iteration stays balanced."""
+        forced = int(os.environ.get("PCL_PAGERANK_CAP", "0"))
+        plans = {cap: pagerank_stream_plan(self.row_ptr, cap) for cap in ((forced,) if forced else (2048, 4096))}
+        if len(plans) == 1 or self.n_edges_local == 0 or not self.edge_balanced:
+            return next(iter(plans.values()))
+        dev = self.device
+        probe = torch.full((self.tables[0].L,), 1.0 / max(self.n, 1), device=dev)
+        out_c, out_r = torch.empty_like(self.rank_local), torch.empty_like(self.rank_local)
+        times = torch.zeros(2, dtype=torch.float64, device=dev)
+        for j, cap in enumerate((2048, 4096)):
+            for rep in range(2):                       # the second launch is the timed one
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                pagerank_pull_stream(self.row_ptr, self.cols, probe, self.inv_outdeg, self.d, self.acc,
+                                     out_c, out_r, None, None, plans[cap])
+                e1.record()
+                torch.cuda.synchronize(dev)
+                times[j] = e0.elapsed_time(e1)
+        if self.world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX, group=self.group)
+        return plans[2048] if float(times[0]) <= float(times[1]) else plans[4096]
 
     def _barrier(self):
         self.paracel_sync()

@@ -56,7 +56,7 @@ SIGS = {
     "pcl_lr_dense_grad": "pppqiippppip",
     "pcl_lr_sparse_grad": "pppppqiippip",
     "pcl_pagerank_pull": "ppppqfppppiqpip",
-    "pcl_pagerank_pull_stream": "ppppqqppfpppppp",
+    "pcl_pagerank_pull_stream": "ppppqqppfpppppip",
     "pcl_lda_gibbs": "ppppppqifffQip",
     "pcl_lda_loglik": "ppppppqifffpp",
     "pcl_als_solve": "pppppppppppqifip",

@@ -47,22 +47,25 @@ def pagerank_pull(row_ptr, cols, contrib, inv_outdeg, damping, new_contrib, new_
               _lib.stream_ptr())
 
 
-PR_CAP = 2048
+PR_CAPS = (2048, 4096)
 
 
-def pagerank_stream_plan(row_ptr):
-    """Static per-graph plan of the edge-balanced kernel: for every block of 2048 in-links the row
-    that holds its first and the row that holds its last in-link (int32 arrays)."""
+def pagerank_stream_plan(row_ptr, cap: int = 2048):
+    """Static per-graph plan of the edge-balanced kernel: for every block of ``cap`` in-links (2048
+    or 4096) the row that holds its first and the row that holds its last in-link (int32 arrays),
+    and ``cap`` itself."""
+    if cap not in PR_CAPS:
+        raise ValueError(f"cap must be one of {PR_CAPS}")
     nnz = int(row_ptr[-1].item())
-    nb = (nnz + PR_CAP - 1) // PR_CAP
+    nb = (nnz + cap - 1) // cap
     if nb == 0:
         z = row_ptr.new_zeros(0, dtype=torch.int32)
-        return z, z
-    starts = torch.arange(nb, device=row_ptr.device, dtype=torch.int64) * PR_CAP
-    lasts = torch.clamp(starts + PR_CAP, max=nnz) - 1
+        return z, z, cap
+    starts = torch.arange(nb, device=row_ptr.device, dtype=torch.int64) * cap
+    lasts = torch.clamp(starts + cap, max=nnz) - 1
     first = torch.searchsorted(row_ptr, starts, right=True) - 1
     last = torch.searchsorted(row_ptr, lasts, right=True) - 1
-    return first.to(torch.int32).contiguous(), last.to(torch.int32).contiguous()
+    return first.to(torch.int32).contiguous(), last.to(torch.int32).contiguous(), cap
 
 
 def pagerank_pull_stream(row_ptr, cols, contrib, inv_outdeg, damping, acc, new_contrib, new_rank=None,
@@ -75,4 +78,4 @@ def pagerank_pull_stream(row_ptr, cols, contrib, inv_outdeg, damping, acc, new_c
         plan = pagerank_stream_plan(row_ptr)
     _lib.call("pcl_pagerank_pull_stream", row_ptr, cols, contrib, inv_outdeg, n, cols.numel(),
               plan[0], plan[1], float(damping), acc, new_contrib, new_rank, delta_l1, old_rank,
-              _lib.stream_ptr())
+              int(plan[2]), _lib.stream_ptr())

@@ -408,8 +408,26 @@ def als_gpu(comm, info, pt):
     m.load(u[keep], i[keep], r[keep],
            torch.as_tensor(np.searchsorted(inames, np.asarray(fid, dtype=np.int64)), device=dev),
            torch.as_tensor(fac.reshape(-1, k), device=dev))
-    m.solve()
-    print("rmse:", m.cal_rmse())
+    if pt.get("validate_input"):
+        # the validate driver (als_validate_driver.cpp:56-86): sweep the lambdas, report the train
+        # and the validation RMSE over the pairs whose user and item are known
+        vu, vi, vr = _my_triples(comm, pt.get("validate_input"), ",")
+        known = np.isin(vu, unames) & np.isin(vi, inames)
+        vu_t = torch.as_tensor(np.searchsorted(unames, vu[known]), device=dev)
+        vi_t = torch.as_tensor(np.searchsorted(inames, vi[known]), device=dev)
+        vr_t = torch.as_tensor(vr[known], device=dev)
+        for lam in pt.get("lambdas", [m.lam]):
+            m.solve(float(lam))
+            train = m.cal_rmse()
+            sse, cnt = m.validate_sse(vu_t, vi_t, vr_t)
+            tot = torch.tensor([sse, cnt], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(tot)
+            if comm.get_rank() == 0:
+                print(f"lambda {lam}: train rmse {train} validate rmse {float((tot[0] / tot[1].clamp(min=1)).sqrt())}")
+    else:
+        m.solve()
+        print("rmse:", m.cal_rmse())
     m.dump_result()
     return m
 
@@ -509,5 +527,5 @@ def mvv_gpu(comm, info, pt):
 
 GPU_ALGORITHMS = {"mf": mf_gpu, "pagerank": pagerank_gpu, "kmeans": kmeans_gpu, "lr": lr_gpu,
                   "ridge": ridge_gpu, "lr_l1": l1_gpu, "lasso": lasso_gpu, "gLDA": lda_gpu, "lda": lda_gpu,
-                  "als": als_gpu, "svd": svd_gpu, "sim_dense": sim_dense_gpu, "ab_sim_dense": sim_dense_gpu,
+                  "als": als_gpu, "als_validate": als_gpu, "svd": svd_gpu, "sim_dense": sim_dense_gpu, "ab_sim_dense": sim_dense_gpu,
                   "sim_sparse": sim_sparse_gpu, "mvv": mvv_gpu}
