@@ -65,16 +65,21 @@ class DeviceSspClock:
                   self.status, self.rank, _lib.stream_ptr())
 
     def check(self):
-        """Synchronise and raise SspTimeout if any wait since the last check expired."""
+        """Synchronise and raise what the status block holds since the last check: SspTimeout for
+        a wait that expired, BadDeviceId when a pull or push that reported through this block met
+        an id outside its table."""
         st = self.status.cpu()
         code = int(st[0].item()) & 0xFFFFFFFF
-        if code != 0:
-            lo = int(st[0].item())
-            rank = (lo >> 32) & 0xFFFFFFFF
-            wait_id = int(st[1].item()) & 0xFFFFFFFF
-            expected, seen = int(st[2].item()), int(st[3].item())
-            self.status.zero_()
-            raise SspTimeout(rank, wait_id, expected, seen)
+        if code == 0:
+            return
+        lo = int(st[0].item())
+        rank = (lo >> 32) & 0xFFFFFFFF
+        wait_id = int(st[1].item()) & 0xFFFFFFFF
+        expected, seen = int(st[2].item()), int(st[3].item())
+        self.status.zero_()
+        if code == 2:
+            raise _lib.BadDeviceId("device table", rank, wait_id, expected, seen)
+        raise SspTimeout(rank, wait_id, expected, seen)
 
     def free(self):
         self.clocks = None
