@@ -24,14 +24,28 @@ from ..parallel.symm import SymmBuffer
 
 
 # "2sm": pairs of CTAs on one 256 x 256 tile (tcgen05 cta_group::2, gemm_tf32_2sm.cu);
-# "1sm": one CTA per 128 x 128 tile (gemm_tf32.cu).
-KERNEL = os.environ.get("PCL_GEMM_KERNEL", "2sm")
+# "1sm": one CTA per 128 x 128 tile (gemm_tf32.cu);
+# "2sm_mc": the pair kernel with clusters of four CTAs that share B through TMA multicast
+#   (csrc/cuda_single/gemm_tf32_2sm_mc.cu).  It exists only where the single-GPU kernel library is
+#   installed, takes local operands only, and is what ``gemm_nt`` / ``argmin_nt`` use by default
+#   in a process that is not part of a multi-rank job; otherwise they use "2sm".
+KERNEL = os.environ.get("PCL_GEMM_KERNEL", "auto")
+
+
+def _single_process() -> bool:
+    return not (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1)
 
 
 def _entry(kernel: Optional[str] = None) -> str:
     k = kernel or KERNEL
-    if k not in ("1sm", "2sm"):
+    if k == "auto":
+        k = "2sm_mc" if (_single_process() and _lib.load_single() is not None) else "2sm"
+    if k not in ("1sm", "2sm", "2sm_mc"):
         raise ValueError(f"unknown GEMM kernel {k!r}")
+    if k == "2sm_mc":
+        if not _single_process():
+            raise ValueError("the multicast GEMM kernel is for single-GPU processes only")
+        return "pcl_gemm_tf32_2sm_mc"
     return "pcl_gemm_tf32_2sm" if k == "2sm" else "pcl_gemm_tf32"
 
 
@@ -91,7 +105,12 @@ def _launch(A, B, C, epi, bnorm, row_min, row_arg, status=None, kernel=None):
         status = _status(A.device)
     N = B.shape[0]
     ldc = C.stride(0) if C is not None else 0
-    _lib.call(_entry(kernel), A, B, C, M, N, K, ldc, epi, bnorm, row_min, row_arg, None, None, 1, 0,
+    entry = _entry(kernel)
+    if entry == "pcl_gemm_tf32_2sm_mc":
+        _lib.call_single(entry, A, B, C, M, N, K, ldc, epi, bnorm, row_min, row_arg, status, 0,
+                         _lib.stream_ptr())
+        return
+    _lib.call(entry, A, B, C, M, N, K, ldc, epi, bnorm, row_min, row_arg, None, None, 1, 0,
               N, 0, 0, status, 0, _lib.stream_ptr())
 
 
@@ -124,7 +143,7 @@ def argmin_nt(A: torch.Tensor, B: torch.Tensor, bnorm: Optional[torch.Tensor] = 
         A2, B2 = split3(_pad_k(A), False), split3(_pad_k(B), True)
     else:
         A2, B2 = _pad_k(A), _pad_k(B)
-    two = _entry(kernel) == "pcl_gemm_tf32_2sm"
+    two = _entry(kernel) != "pcl_gemm_tf32"
     row_min = torch.empty((2, M) if two else (M,), device=A.device, dtype=torch.float32)
     row_arg = torch.empty((2, M) if two else (M,), device=A.device, dtype=torch.int32)
     _launch(A2, B2, None, 1, bnorm, row_min, row_arg, kernel=kernel)
@@ -156,7 +175,9 @@ class DenseReadGemm:
         self.status = torch.zeros(4, dtype=torch.int64, device=self.device)
         self.epoch = 0
         self.gather_ctas = gather_ctas
-        self.entry = _entry(kernel)
+        k = kernel or KERNEL
+        # the shards may be peers' memory: never the multicast kernel here
+        self.entry = _entry("2sm" if k in ("auto", "2sm_mc") else k)
 
     def local_rows(self) -> Tuple[int, int]:
         lo = self.rank * self.rps
