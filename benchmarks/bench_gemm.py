@@ -36,10 +36,8 @@ def main():
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=128)
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--kernel", default="auto", choices=["auto", "1sm", "2sm", "2sm_mc"],
-                    help="1sm: one CTA per 128x128 tile; 2sm: CTA pairs on 256x256 tiles; 2sm_mc: pairs in "
-                         "clusters of four sharing B by multicast (single-GPU library); auto: 2sm_mc "
-                         "where installed, else 2sm")
+    ap.add_argument("--kernel", default="2sm", choices=["1sm", "2sm"],
+                    help="1sm: one CTA per 128x128 tile; 2sm: CTA pairs on 256x256 / 256x512 items")
     args = ap.parse_args()
     from paracel_b200.ops.gemm import argmin_nt, check_status, gemm_nt
     dev = "cuda"

@@ -68,25 +68,16 @@ def kernels_path() -> Path:
     return LIB / "libpcl_kernels.so"
 
 
-def single_path() -> Path:
-    """Kernels that only a process driving ONE GPU with local operands may use (``csrc/cuda_single``:
-    cluster-multicast operand loads).  Source and library are optional: where they are absent
-    the package runs on the kernels of ``libpcl_kernels.so`` alone."""
-    return LIB / "libpcl_kernels_single.so"
-
-
 def core_path() -> Path:
     return LIB / ("_pcl_core" + sysconfig.get_config_var("EXT_SUFFIX"))
 
 
-def build_kernels(force=False, verbose=False, ptxas_v=False, single=False) -> Path:
+def build_kernels(force=False, verbose=False, ptxas_v=False) -> Path:
     LIB.mkdir(exist_ok=True)
     OBJ.mkdir(exist_ok=True)
-    cu = sorted((CSRC / ("cuda_single" if single else "cuda")).glob("*.cu"))
+    cu = sorted((CSRC / "cuda").glob("*.cu"))
     hdr = sorted((CSRC / "cuda").glob("*.cuh")) + sorted((CSRC / "cuda").glob("*.h"))
-    out = single_path() if single else kernels_path()
-    if single and not cu:
-        return out
+    out = kernels_path()
     hdr_stamp = _stamp(hdr, " ".join(NVCC_FLAGS))
     nvcc = _nvcc()
     jobs = []
@@ -146,7 +137,6 @@ def build_core(force=False, verbose=False) -> Path:
 
 def build_all(force=False, verbose=False):
     k = build_kernels(force=force, verbose=verbose)
-    build_kernels(force=force, verbose=verbose, single=True)
     c = build_core(force=force, verbose=verbose)
     return k, c
 
@@ -155,6 +145,5 @@ if __name__ == "__main__":
     force = "--force" in sys.argv
     if "--ptxas" in sys.argv:
         build_kernels(force=True, ptxas_v=True)
-        build_kernels(force=True, ptxas_v=True, single=True)
     else:
         print(build_all(force=force, verbose="-v" in sys.argv))

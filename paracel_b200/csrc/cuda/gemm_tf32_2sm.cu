@@ -13,6 +13,13 @@
 // alg/clustering/kmeans/kmeans.hpp:113-133 and the all-pairs products of
 // alg/recommendation/similarity_dense/sim_dense.hpp:84-101.
 //
+// Two item forms, chosen by the launcher:
+//   256 x 256 items, two accumulators that alternate (the epilogue of one tile runs under the
+//     main loop of the next), six 32 KB operand stages per CTA;
+//   256 x 512 items, two accumulators fed from the same A stage (24 KB instead of 32 KB of
+//     operands per 256 x 256 x 32 block of MACs), four 48 KB stages; the epilogue of an item
+//     overlaps only with the operand prefetch of the next, so this form pays for long K only.
+//
 // Roles in each CTA (320 threads):
 //   warp 0      TMA producer for this CTA's operand halves; the transfers of both
 //               CTAs complete on the LEADER's "full" barrier (cta_group::2 form of
@@ -24,13 +31,12 @@
 //               32 x 32 chunk is in flight while the current one is written, with the
 //               128-byte swizzle, into the warp's staging buffer and handed to a bulk tensor
 //               store (cp.async.bulk.tensor shared -> global, local memory; stores have no
-//               multicast form), which clips at the edges of C; or the arg-min.  Measured:
-//               six operand stages with one 4 KB staging buffer per warp beat five stages with
-//               two buffers on every shape (the main loop is bound by operand latency out of
-//               L2, the store engine is not the limit).  The accumulator buffer is released as soon as its last chunk is in
-//               registers.  With K = 512 a tile's MMAs take about 4 us; four epilogue warps
-//               with per-row global stores needed about 8 us per tile and held the tensor
-//               cores back.
+//               multicast form), which clips at the edges of C; or the arg-min.  The
+//               accumulator is released as soon as its last chunk is in registers.
+// Measured and not kept for the epilogue: two staging buffers per warp with five operand stages
+// (slower on every shape), coalesced 128-bit global stores out of the staging buffer (8 % slower),
+// 256-bit stores straight from the registers (17 % slower), L2 evict-first / evict-last hints on
+// the C stores and the B loads (within 2 %), a start-up stagger between the pairs (no change).
 // Every wait has a time limit; on expiry the status record is written, both
 // CTAs of the pair are told to leave, tensor memory is freed and the kernel ends.
 #include <cuda.h>
@@ -43,19 +49,19 @@ namespace {
 using namespace pcl_sm100;
 
 constexpr int TM = 256;      // tile rows per CTA pair
-constexpr int TN = 256;      // tile columns
+constexpr int TN = 256;      // columns per accumulator
 constexpr int HM = 128;      // rows of A (and of the accumulator) per CTA
-constexpr int HN = 128;      // rows of B staged per CTA
+constexpr int HN = 128;      // rows of B staged per CTA and accumulator
 constexpr int BK = 32;       // 32 fp32 = 128 bytes = one swizzle row
-constexpr int STAGES = 6;
 constexpr int UMMA_K = 8;
 constexpr int A_BYTES = HM * BK * 4;
 constexpr int B_BYTES = HN * BK * 4;
+constexpr int OPERAND_BYTES = 6 * (A_BYTES + B_BYTES);   // 192 KB of operand stages in either form
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
-constexpr int EPI_BUFS = 1;  // staging buffers per epilogue warp (4 KB each)
-constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * 32 * 128;
-constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int EPI_BYTES = EPI_WARPS * 32 * 128;           // one 4 KB staging buffer per epilogue warp
+constexpr int SMEM_BYTES = OPERAND_BYTES + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int MAX_STAGES = 6;
 
 struct Gemm2Args {
   float* C;
@@ -69,27 +75,65 @@ struct Gemm2Args {
   float* b_stage;
   int* flags;          // one per 256-column tile
   int world, rank, rows_per_shard, epoch, gather_ctas;
+  int group;           // row blocks per raster group (0: row-block major)
   PclStatus* status;
 };
-
 
 __device__ __forceinline__ int tile_at(int ord, int n_tiles, int first_local) {
   const int t = first_local + ord;
   return t >= n_tiles ? t - n_tiles : t;
 }
 
-__device__ __forceinline__ void decode_item(long long item, bool flat, int n_tiles, int n_first,
-                                            long long first_items, int& mt, int& ord0, int& ord1) {
-  if (!flat) {
-    mt = (int)item; ord0 = 0; ord1 = n_tiles;
-  } else if (item < first_items) {
-    mt = (int)(item / n_first); ord0 = (int)(item % n_first); ord1 = ord0 + 1;
-  } else {
-    const long long rem = item - first_items;
-    const int n_rest = n_tiles - n_first;
-    mt = (int)(rem / n_rest); ord0 = n_first + (int)(rem % n_rest); ord1 = ord0 + 1;
+// The order in which a pair walks the output.  A work item is a 256-row block `mt` with the
+// column tiles of positions [ord0, ord1) of the rank's tile order (tile_at): NH of them with a
+// stored C, all of them with the arg-min epilogue (the caller then steps through them NH at a time).
+template <int NH>
+struct Schedule {
+  bool flat;
+  int n_tiles, m_tiles, n_first, ipr1, ipr2, group;
+  long long first_items, items;
+
+  __device__ Schedule(const Gemm2Args& a, int n_tiles_, int m_tiles_) {
+    flat = (a.epi == 0);
+    n_tiles = n_tiles_;
+    m_tiles = m_tiles_;
+    // With a fused gather the stored form has two phases: every row block against this rank's own
+    // column tiles first (their staging is a local copy), then against the tiles of the peers.
+    n_first = n_tiles;
+    if (a.gather_ctas > 0) {
+      const int own_rows = max(0, min(a.rows_per_shard, a.N - a.rank * a.rows_per_shard));
+      n_first = max(1, min(n_tiles, own_rows / TN));
+    }
+    ipr1 = (n_first + NH - 1) / NH;
+    ipr2 = (n_tiles - n_first + NH - 1) / NH;
+    group = (flat && a.gather_ctas == 0) ? a.group : 0;
+    first_items = (long long)m_tiles * ipr1;
+    items = flat ? (long long)m_tiles * (ipr1 + ipr2) : (long long)m_tiles;
   }
-}
+
+  __device__ void decode(long long item, int& mt, int& ord0, int& ord1) const {
+    if (!flat) {
+      mt = (int)item; ord0 = 0; ord1 = n_tiles;
+    } else if (group > 0) {
+      // groups of `group` row blocks, column-tile major inside a group: the pairs that run together
+      // then touch `group` row blocks of A and about (pairs / group) tiles of B instead of one
+      // row block and every tile of B
+      const long long per = (long long)group * ipr1;
+      const long long g = item / per;
+      const int r = (int)(item - g * per);
+      const int rows = (int)min((long long)group, (long long)m_tiles - g * group);
+      mt = (int)(g * group) + r % rows;
+      ord0 = (r / rows) * NH; ord1 = min(ord0 + NH, n_tiles);
+    } else if (item < first_items) {
+      mt = (int)(item / ipr1);
+      ord0 = (int)(item % ipr1) * NH; ord1 = min(ord0 + NH, n_first);
+    } else {
+      const long long rem = item - first_items;
+      mt = (int)(rem / ipr2);
+      ord0 = n_first + (int)(rem % ipr2) * NH; ord1 = min(ord0 + NH, n_tiles);
+    }
+  }
+};
 
 // raise the abort flag of both CTAs of the pair
 __device__ __forceinline__ void abort_pair(volatile int* abort_flag, uint32_t peer) {
@@ -99,9 +143,16 @@ __device__ __forceinline__ void abort_pair(volatile int* abort_flag, uint32_t pe
                : "memory");
 }
 
+// NH = 1: one 256 x 256 accumulator per item, two of them alternate (the epilogue of a tile runs
+//         under the main loop of the next), six 32 KB operand stages per CTA.
+// NH = 2: a 256 x 512 item, both accumulators fed from the same A stage; four 48 KB stages.
+template <int NH>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmC, Gemm2Args a) {
+  constexpr int STAGES = (NH == 2) ? 4 : 6;
+  constexpr int STAGE_BYTES = A_BYTES + NH * B_BYTES;
+  static_assert(STAGES * STAGE_BYTES == OPERAND_BYTES, "operand stages fill the same 192 KB");
   extern __shared__ uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = (a.N + TN - 1) / TN;
@@ -109,6 +160,7 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int kb_count = (a.K + BK - 1) / BK;
   int first_local = 0;
   if (a.world > 1) first_local = (int)(((long long)a.rank * a.rows_per_shard) / TN) % n_tiles;
+
 
   // ------------------------------------------------- gather CTAs (whole clusters)
   // One thread per gather CTA drives the copy engine of its SM: contiguous pieces of a peer's
@@ -208,18 +260,18 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     return;
   }
 
+
   // ------------------------------------------------------------------ MMA pairs
   const uint32_t me = cluster_ctarank();   // 0 = leader
   const uint32_t peer = me ^ 1u;
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sA = base;
-  uint8_t* sB = base + STAGES * A_BYTES;
-  uint8_t* sE = base + STAGES * (A_BYTES + B_BYTES);
+  uint8_t* sOp = base;                   // stage s: A at s * STAGE_BYTES, B of accumulator h behind it
+  uint8_t* sE = base + OPERAND_BYTES;
   uint64_t* bars = (uint64_t*)(sE + EPI_BYTES);
-  uint64_t* full = bars;                 // STAGES, used in the leader
-  uint64_t* empty = bars + STAGES;       // STAGES, one set per CTA
-  uint64_t* tfull = bars + 2 * STAGES;   // 2, one set per CTA
-  uint64_t* tempty = tfull + 2;          // 2, used in the leader (one arrival per epilogue warp of the pair)
+  uint64_t* full = bars;                     // STAGES, used in the leader
+  uint64_t* empty = bars + MAX_STAGES;       // STAGES, one set per CTA
+  uint64_t* tfull = bars + 2 * MAX_STAGES;   // 2, one set per CTA
+  uint64_t* tempty = tfull + 2;              // 2, used in the leader (one arrival per epilogue warp of the pair)
   uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -242,45 +294,43 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
   const int pair = ((int)blockIdx.x - a.gather_ctas) >> 1;
   const int npair = ((int)gridDim.x - a.gather_ctas) >> 1;
-  // Work items: with a stored C every 256 x 256 tile is an item (row-block major, so the pairs
-  // that run together share A and all of B through L2); with the arg-min epilogue an item is a
-  // 256-row block whose pair walks all column tiles (running minimum; local tiles first).
-  const bool flat = (a.epi == 0);
-  const long long items = flat ? (long long)m_tiles * n_tiles : (long long)m_tiles;
-  // With a fused gather the flat order has two phases: every row block against this rank's own
-  // column tiles first (they need no staging), then every row block against the staged tiles.
-  int n_first = n_tiles;
-  if (a.gather_ctas > 0) {
-    const int own_rows = max(0, min(a.rows_per_shard, a.N - a.rank * a.rows_per_shard));
-    n_first = max(1, min(n_tiles, own_rows / TN));
-  }
-  const long long first_items = (long long)m_tiles * n_first;
+  const Schedule<NH> sch(a, n_tiles, m_tiles);
 
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long item = pair; item < items && ok; item += npair) {
+      for (long long item = pair; item < sch.items && ok; item += npair) {
         int mt, ord0, ord1;
-        decode_item(item, flat, n_tiles, n_first, first_items, mt, ord0, ord1);
-        for (int ord = ord0; ord < ord1 && ok; ++ord) {
-          const int nt = tile_at(ord, n_tiles, first_local);
+        sch.decode(item, mt, ord0, ord1);
+        for (int ord = ord0; ord < ord1 && ok; ord += NH) {
+          int nts[NH];
+          int nvalid = 0;
+#pragma unroll
+          for (int h = 0; h < NH; ++h) {
+            nts[h] = (ord + h < ord1) ? tile_at(ord + h, n_tiles, first_local) : -1;
+            nvalid += nts[h] >= 0;
+          }
           if (a.gather_ctas > 0) {
-            int seen = 0;
-            const unsigned long long t0 = pcl_globaltimer();
-            for (unsigned it = 0;; ++it) {
-              seen = pcl_ld_acquire_sys_i32(a.flags + nt);
-              if (seen == a.epoch || *abort_flag) break;
-              if ((it & 15) == 15 && pcl_globaltimer() - t0 > WAIT_NS) break;
-              __nanosleep(128);
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+              if (nts[h] < 0 || !ok) continue;
+              int seen = 0;
+              const unsigned long long t0 = pcl_globaltimer();
+              for (unsigned it = 0;; ++it) {
+                seen = pcl_ld_acquire_sys_i32(a.flags + nts[h]);
+                if (seen == a.epoch || *abort_flag) break;
+                if ((it & 15) == 15 && pcl_globaltimer() - t0 > WAIT_NS) break;
+                __nanosleep(128);
+              }
+              if (seen != a.epoch) {
+                report(a.status, a.rank, 30, a.epoch, seen);
+                abort_pair(abort_flag, peer);
+                ok = false;
+              }
             }
-            if (seen != a.epoch) {
-              report(a.status, a.rank, 30, a.epoch, seen);
-              abort_pair(abort_flag, peer);
-              ok = false;
-              break;
-            }
+            if (!ok) break;
             asm volatile("fence.proxy.async;" ::: "memory");
           }
           for (int kb = 0; kb < kb_count; ++kb) {
@@ -290,12 +340,15 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
               ok = false;
               break;
             }
-            if (me == 0) mbar_expect_tx(full + stage, 2 * (A_BYTES + B_BYTES));
+            if (me == 0) mbar_expect_tx(full + stage, 2u * (uint32_t)(A_BYTES + nvalid * B_BYTES));
             const uint32_t lbar = map_to_cta(smem_u32(full + stage), 0);
-            tma_load_2d_pair(map_to_cta(smem_u32(sA + stage * A_BYTES), me), &tmA, lbar, kb * BK,
-                             mt * TM + (int)me * HM);
-            tma_load_2d_pair(map_to_cta(smem_u32(sB + stage * B_BYTES), me), &tmB, lbar, kb * BK,
-                             nt * TN + (int)me * HN);
+            uint8_t* st = sOp + stage * STAGE_BYTES;
+            tma_load_2d_pair(map_to_cta(smem_u32(st), me), &tmA, lbar, kb * BK, mt * TM + (int)me * HM);
+#pragma unroll
+            for (int h = 0; h < NH; ++h)
+              if (nts[h] >= 0)
+                tma_load_2d_pair(map_to_cta(smem_u32(st + A_BYTES + h * B_BYTES), me), &tmB, lbar, kb * BK,
+                                 nts[h] * TN + (int)me * HN);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         }
@@ -313,19 +366,11 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       int acc = 0;
       uint32_t acc_phase[2] = {0, 0};
       bool ok = true;
-      for (long long item = pair; item < items && ok; item += npair) {
+      for (long long item = pair; item < sch.items && ok; item += npair) {
         int mt, ord0, ord1;
-        decode_item(item, flat, n_tiles, n_first, first_items, mt, ord0, ord1);
-        for (int ord = ord0; ord < ord1 && ok; ++ord) {
-          if (!mbar_wait(tempty + acc, acc_phase[acc] ^ 1, abort_flag)) {
-            report(a.status, a.rank, 32, acc, 0);
-            abort_pair(abort_flag, peer);
-            ok = false;
-            break;
-          }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t d = tmem_base + (uint32_t)(acc * TN);
-          for (int kb = 0; kb < kb_count; ++kb) {
+        sch.decode(item, mt, ord0, ord1);
+        for (int ord = ord0; ord < ord1 && ok; ord += NH) {
+          for (int kb = 0; kb < kb_count && ok; ++kb) {
             if (!mbar_wait(full + stage, phase, abort_flag)) {
               report(a.status, a.rank, 33, kb, stage);
               abort_pair(abort_flag, peer);
@@ -333,146 +378,162 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
               break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t da = make_desc_sw128(smem_u32(sA + stage * A_BYTES));
-            const uint64_t db = make_desc_sw128(smem_u32(sB + stage * B_BYTES));
+            uint8_t* st = sOp + stage * STAGE_BYTES;
+            const uint64_t da = make_desc_sw128(smem_u32(st));
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)
-              umma_tf32_pair(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
-                             (kb > 0 || k > 0) ? 1u : 0u);
+            for (int h = 0; h < NH; ++h) {
+              if (ord + h >= ord1) continue;
+              const int slot = (NH == 2) ? h : acc;
+              if (kb == 0) {   // the epilogue has drained what this accumulator held before
+                if (!mbar_wait(tempty + slot, acc_phase[slot] ^ 1, abort_flag)) {
+                  report(a.status, a.rank, 32, slot, 0);
+                  abort_pair(abort_flag, peer);
+                  ok = false;
+                  break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+              }
+              const uint32_t d = tmem_base + (uint32_t)(slot * TN);
+              const uint64_t db = make_desc_sw128(smem_u32(st + A_BYTES + h * B_BYTES));
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                umma_tf32_pair(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                               (kb > 0 || k > 0) ? 1u : 0u);
+              if (kb == kb_count - 1) {   // this accumulator is complete once these MMAs are
+                umma_commit_pair(map_to_cta(smem_u32(tfull + slot), 0));
+                umma_commit_pair(map_to_cta(smem_u32(tfull + slot), 1));
+                acc_phase[slot] ^= 1;
+              }
+            }
+            if (!ok) break;
             // free this stage in both CTAs
             umma_commit_pair(map_to_cta(smem_u32(empty + stage), 0));
             umma_commit_pair(map_to_cta(smem_u32(empty + stage), 1));
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
-          if (!ok) break;
-          umma_commit_pair(map_to_cta(smem_u32(tfull + acc), 0));
-          umma_commit_pair(map_to_cta(smem_u32(tfull + acc), 1));
-          acc_phase[acc] ^= 1;
-          acc ^= 1;
+          if (NH == 1) acc ^= 1;
         }
       }
     }
   } else {
     const int sub = warp & 3;                 // tensor-memory sub-partition of this warp
-    const int half = (warp - 2) >> 2;         // which 128 of the tile's 256 columns
+    const int half = (warp - 2) >> 2;         // which 128 of the accumulator's 256 columns
     constexpr int HC = TN / 2;                // columns per epilogue warp
-    float* stg = reinterpret_cast<float*>(sE + (warp - 2) * (EPI_BUFS * 4096));
-    unsigned stores = 0;                                              // bulk stores issued by this warp
+    float* stg = reinterpret_cast<float*>(sE + (warp - 2) * 4096);
     const uint32_t tempty_leader0 = map_to_cta(smem_u32(tempty), 0);
+    const bool vec_ok = ((a.ldc & 3) == 0) && ((((uintptr_t)a.C) & 15) == 0);
     int acc = 0;
     uint32_t acc_phase[2] = {0, 0};
     bool ok = true;
-    for (long long item = pair; item < items && ok; item += npair) {
+    for (long long item = pair; item < sch.items && ok; item += npair) {
       int mt, ord0, ord1;
-      decode_item(item, flat, n_tiles, n_first, first_items, mt, ord0, ord1);
+      sch.decode(item, mt, ord0, ord1);
       const int row_base = mt * TM + (int)me * HM + sub * 32;   // first row of this warp's 32
       const int row = row_base + lane;
       float best = 3.402823466e38f;
       int best_n = 0;
-      for (int ord = ord0; ord < ord1 && ok; ++ord) {
-        const int nt = tile_at(ord, n_tiles, first_local);
-        if (!mbar_wait(tfull + acc, acc_phase[acc], abort_flag)) {
-          if (lane == 0) {
-            report(a.status, a.rank, 34, acc, 0);
-            abort_pair(abort_flag, peer);
+      for (int ord = ord0; ord < ord1 && ok; ord += NH) {
+#pragma unroll 1
+        for (int h = 0; h < NH; ++h) {
+          if (ord + h >= ord1 || !ok) continue;
+          const int nt = tile_at(ord + h, n_tiles, first_local);
+          const int slot = (NH == 2) ? h : acc;
+          if (!mbar_wait(tfull + slot, acc_phase[slot], abort_flag)) {
+            if (lane == 0) {
+              report(a.status, a.rank, 34, slot, 0);
+              abort_pair(abort_flag, peer);
+            }
+            ok = false;
+            break;
           }
-          ok = false;
-          break;
-        }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t t0 = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(acc * TN);
-        const bool vec_ok = ((a.ldc & 3) == 0) && ((((uintptr_t)a.C) & 15) == 0);
-        if (a.epi == 1) {   // |b_n|^2 of this tile's columns, +inf beyond N
-          __syncwarp();
-          for (int q = lane; q < HC; q += 32) {
-            const int n = nt * TN + half * HC + q;
-            stg[q] = n < a.N ? __ldg(a.bnorm + n) : 3.402823466e38f;
-          }
-          __syncwarp();
-        }
-        uint32_t rv[2][32];
-        tmem_ld32_issue(t0 + (uint32_t)(half * HC), rv[0]);
-#pragma unroll
-        for (int c = 0; c < HC / 32; ++c) {
-          uint32_t* cur = rv[c & 1];
-          tmem_ld_wait(cur);
-          if (c + 1 < HC / 32) {
-            tmem_ld32_issue(t0 + (uint32_t)(half * HC + (c + 1) * 32), rv[(c + 1) & 1]);
-          } else {
-            // the last chunk is in registers: hand the accumulator buffer back before its stores
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t t0 = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(slot * TN);
+          if (a.epi == 1) {   // |b_n|^2 of this tile's columns, +inf beyond N
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(tempty_leader0 + (uint32_t)(acc * 8));
+            for (int q = lane; q < HC; q += 32) {
+              const int n = nt * TN + half * HC + q;
+              stg[q] = n < a.N ? __ldg(a.bnorm + n) : 3.402823466e38f;
+            }
+            __syncwarp();
           }
-          float v[32];
+          uint32_t rv[2][32];
+          tmem_ld32_issue(t0 + (uint32_t)(half * HC), rv[0]);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(cur[j]);
-          const int n0 = nt * TN + half * HC + c * 32;
-          if (n0 >= a.N) continue;
-          if (a.epi == 0) {
-            if (vec_ok) {
-              // lane r writes accumulator row r into the staging buffer with the 128-byte swizzle
-              // (16-byte chunk q of row r sits at chunk q ^ (r & 7)); one bulk tensor store then
-              // moves the 32 x 32 box to C.  A buffer is free again once the store that read it
-              // last has finished reading (all earlier stores with one buffer, all but the latest
-              // with two).
-              float* buf = stg + (stores % EPI_BUFS) * 1024;
-              if (lane == 0) {
-                if (EPI_BUFS == 1) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          for (int c = 0; c < HC / 32; ++c) {
+            uint32_t* cur = rv[c & 1];
+            tmem_ld_wait(cur);
+            if (c + 1 < HC / 32) {
+              tmem_ld32_issue(t0 + (uint32_t)(half * HC + (c + 1) * 32), rv[(c + 1) & 1]);
+            } else {
+              // the last chunk is in registers: hand the accumulator back before its stores
+              asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster(tempty_leader0 + (uint32_t)(slot * 8));
+            }
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(cur[j]);
+            const int n0 = nt * TN + half * HC + c * 32;
+            if (n0 >= a.N) continue;
+            if (a.epi == 0) {
+              if (vec_ok) {
+                // lane r writes accumulator row r into the staging buffer with the 128-byte swizzle
+                // (16-byte chunk q of row r sits at chunk q ^ (r & 7)); one bulk tensor store then
+                // moves the 32 x 32 box to C.  The buffer is free again once the store that read it
+                // last has finished reading.
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                __syncwarp();
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                  *reinterpret_cast<float4*>(stg + lane * 32 + ((q ^ (lane & 7)) << 2)) =
+                      make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) tma_store_2d(&tmC, smem_u32(stg), n0, row_base);
+              } else if (row < a.M) {
+                float* dst = a.C + (long long)row * a.ldc + n0;
+                for (int j = 0; j < 32; ++j)
+                  if (n0 + j < a.N) dst[j] = v[j];
               }
-              __syncwarp();
+            } else {
+              // dist[j] = |b_n|^2 - 2 a.b_n; the minimum first (one FMNMX per column), the column
+              // index only when this chunk improves the running best, which becomes rare quickly
+              float d[32];
 #pragma unroll
-              for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<float4*>(buf + lane * 32 + ((q ^ (lane & 7)) << 2)) =
-                    make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-              __syncwarp();
-              if (lane == 0) tma_store_2d(&tmC, smem_u32(buf), n0, row_base);
-              ++stores;
-            } else if (row < a.M) {
-              float* dst = a.C + (long long)row * a.ldc + n0;
-              for (int j = 0; j < 32; ++j)
-                if (n0 + j < a.N) dst[j] = v[j];
-            }
-          } else {
-            // dist[j] = |b_n|^2 - 2 a.b_n; the minimum first (one FMNMX per column), the column
-            // index only when this chunk improves the running best, which becomes rare quickly
-            float d[32];
+              for (int q = 0; q < 8; ++q) {
+                const float4 b = *reinterpret_cast<const float4*>(stg + c * 32 + 4 * q);
+                d[4 * q] = fmaf(-2.f, v[4 * q], b.x);
+                d[4 * q + 1] = fmaf(-2.f, v[4 * q + 1], b.y);
+                d[4 * q + 2] = fmaf(-2.f, v[4 * q + 2], b.z);
+                d[4 * q + 3] = fmaf(-2.f, v[4 * q + 3], b.w);
+              }
+              float m16[16];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              const float4 b = *reinterpret_cast<const float4*>(stg + c * 32 + 4 * q);
-              d[4 * q] = fmaf(-2.f, v[4 * q], b.x);
-              d[4 * q + 1] = fmaf(-2.f, v[4 * q + 1], b.y);
-              d[4 * q + 2] = fmaf(-2.f, v[4 * q + 2], b.z);
-              d[4 * q + 3] = fmaf(-2.f, v[4 * q + 3], b.w);
-            }
-            float m16[16];
+              for (int j = 0; j < 16; ++j) m16[j] = fminf(d[j], d[j + 16]);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) m16[j] = fminf(d[j], d[j + 16]);
+              for (int w = 8; w >= 1; w >>= 1)
 #pragma unroll
-            for (int w = 8; w >= 1; w >>= 1)
+                for (int j = 0; j < w; ++j) m16[j] = fminf(m16[j], m16[j + w]);
+              const float m = m16[0];
+              if (m <= best) {
+                int jn = 31;
 #pragma unroll
-              for (int j = 0; j < w; ++j) m16[j] = fminf(m16[j], m16[j + w]);
-            const float m = m16[0];
-            if (m <= best) {
-              int jn = 31;
-#pragma unroll
-              for (int j = 30; j >= 0; --j) jn = (d[j] == m) ? j : jn;
-              const int n = n0 + jn;
-              if (m < best || n < best_n) { best = m; best_n = n; }
+                for (int j = 30; j >= 0; --j) jn = (d[j] == m) ? j : jn;
+                const int n = n0 + jn;
+                if (m < best || n < best_n) { best = m; best_n = n; }
+              }
             }
           }
+          acc_phase[slot] ^= 1;
         }
-        acc_phase[acc] ^= 1;
-        acc ^= 1;
+        if (NH == 1) acc ^= 1;
       }
       if (ok && a.epi == 1 && row < a.M) {   // one result per column half; the caller merges the two
         a.row_min[(long long)half * a.M + row] = best;
         a.row_arg[(long long)half * a.M + row] = best_n;
       }
     }
-    // the staging buffers must stay intact until the copy engine has read them
+    // the staging buffer must stay intact until the copy engine has read it
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     __syncwarp();
   }
@@ -488,19 +549,63 @@ gemm_tf32_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   }
 }
 
+template <int NH>
+int launch_2sm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, Gemm2Args& a,
+               int num_sms, cudaStream_t stream) {
+  auto kern = gemm_tf32_2sm_kernel<NH>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // every cluster of the grid must be resident at once: MMA pairs wait for the gather CTAs
+  static int max_clusters = -1;
+  if (max_clusters < 0) {
+    cfg.gridDim = dim3(2, 1, 1);
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess) return (int)e;
+    max_clusters = n;
+  }
+  int clusters = max_clusters;
+  if (num_sms > 0 && num_sms / 2 < clusters) clusters = num_sms / 2;
+  if (clusters < 1 + a.gather_ctas / 2) return (int)cudaErrorNotSupported;
+  const int m_tiles = (a.M + TM - 1) / TM;
+  const int n_tiles = (a.N + TN - 1) / TN;
+  int mma_pairs = clusters - a.gather_ctas / 2;
+  // an upper bound of the number of work items (the two-phase order of the fused gather can split
+  // a row block's tiles into one more item than ceil(n_tiles / NH))
+  const long long n_items = (a.epi == 0) ? (long long)m_tiles * ((n_tiles + NH - 1) / NH + 1) : (long long)m_tiles;
+  if (mma_pairs > n_items) mma_pairs = (int)n_items;
+  cfg.gridDim = dim3((unsigned)(a.gather_ctas + 2 * mma_pairs), 1, 1);
+  e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, a);
+  if (e != cudaSuccess) return (int)e;
+  return pcl_last_error();
+}
 
 }  // namespace
 
 // Same arguments as pcl_gemm_tf32, except that `flags` holds one int per 256-column tile,
 // `gather_ctas` is rounded up to an even number, and with epi 1 row_min / row_arg hold 2 x M
 // entries: [0..M) is the result over columns n with (n mod 256) < 128, [M..2M) over the others
-// (the two epilogue warps of a row work on separate column halves; the caller takes the smaller).  Returns cudaErrorNotSupported when the
-// device cannot co-schedule a single pair of CTAs with this much shared memory.
+// (the two epilogue warps of a row work on separate column halves; the caller takes the smaller).
+// `wide`: 1 = 256 x 512 items (two accumulators fed from one A stage), 0 = 256 x 256 items with
+// alternating accumulators, -1 = chosen here (wide for K >= 1024 with at least two column tiles).
+// Returns cudaErrorNotSupported when the device cannot co-schedule a single pair of CTAs with
+// this much shared memory.
 PCL_API int pcl_gemm_tf32_2sm(const float* A, float* b_stage, float* C, int M, int N, int K,
                               long long ldc, int epi, const float* bnorm, float* row_min, int* row_arg,
                               const float* const* b_shards, int* flags, int world, int rank,
                               int rows_per_shard, int epoch, int gather_ctas, PclStatus* status,
-                              int num_sms, cudaStream_t stream) {
+                              int num_sms, int wide, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K & 3) || ((uintptr_t)A & 15) || ((uintptr_t)b_stage & 15)) return (int)cudaErrorInvalidValue;
   if (epi == 0 && C == nullptr) return (int)cudaErrorInvalidValue;
@@ -525,39 +630,13 @@ PCL_API int pcl_gemm_tf32_2sm(const float* A, float* b_stage, float* C, int M, i
   const bool fused = (world > 1 && b_shards != nullptr);
   a.gather_ctas = fused ? (gather_ctas > 0 ? ((gather_ctas + 1) & ~1) : 16) : 0;
   if (fused && flags == nullptr) return (int)cudaErrorInvalidValue;
-
-  cudaError_t e = cudaFuncSetAttribute(gemm_tf32_2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       SMEM_BYTES);
-  if (e != cudaSuccess) return (int)e;
-  cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(THREADS, 1, 1);
-  cfg.dynamicSmemBytes = SMEM_BYTES;
-  cfg.stream = stream;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  // every cluster of the grid must be resident at once: MMA pairs wait for the gather CTAs
-  static int max_clusters = -1;
-  if (max_clusters < 0) {
-    cfg.gridDim = dim3(2, 1, 1);
-    int n = 0;
-    e = cudaOccupancyMaxActiveClusters(&n, gemm_tf32_2sm_kernel, &cfg);
-    if (e != cudaSuccess) return (int)e;
-    max_clusters = n;
-  }
-  int clusters = max_clusters;
-  if (num_sms > 0 && num_sms / 2 < clusters) clusters = num_sms / 2;
-  if (clusters < 1 + a.gather_ctas / 2) return (int)cudaErrorNotSupported;
-  const int m_tiles = (M + TM - 1) / TM;
-  int mma_pairs = clusters - a.gather_ctas / 2;
-  const long long n_items = (epi == 0) ? (long long)m_tiles * ((N + TN - 1) / TN) : (long long)m_tiles;
-  if (mma_pairs > n_items) mma_pairs = (int)n_items;
-  cfg.gridDim = dim3((unsigned)(a.gather_ctas + 2 * mma_pairs), 1, 1);
-  e = cudaLaunchKernelEx(&cfg, gemm_tf32_2sm_kernel, tmA, tmB, tmC, a);
-  if (e != cudaSuccess) return (int)e;
-  return pcl_last_error();
+  // Measured on 65536 x 16384 and 8192 x 8192 outputs, the forms interleaved in one process:
+  // K = 512: 566 TFLOP/s with 256 x 256 items, 509 with 256 x 512; K = 1024: 406 against 594;
+  // K = 8192: 550 against 619, and 667 with raster groups.  Groups of eight row blocks pay once B
+  // is larger than the L2 cache (K = 8192: B is 268 MB) and cost up to a tenth below that.
+  a.group = ((long long)N * K * 4 >= (100ll << 20)) ? 8 : 0;
+  const int n_tiles = (N + TN - 1) / TN;
+  if (wide < 0) wide = (n_tiles >= 2 && K >= 1024) ? 1 : 0;
+  return wide ? launch_2sm<2>(tmA, tmB, tmC, a, num_sms, stream)
+              : launch_2sm<1>(tmA, tmB, tmC, a, num_sms, stream);
 }

@@ -46,7 +46,7 @@ SIGS = {
     "pcl_mf_sgd_pass_h16": "pppqppppppfffiifippppipip",
     "pcl_mf_sse": "pppqppppifppp",
     "pcl_gemm_tf32": "pppiiiqipppppiiiiipip",
-    "pcl_gemm_tf32_2sm": "pppiiiqipppppiiiiipip",
+    "pcl_gemm_tf32_2sm": "pppiiiqipppppiiiiipiip",
     "pcl_split3_tf32": "ppqiip",
     "pcl_dense_read": "ppqqiipqQpp",
     "pcl_dense_bupdate": "ppqqiiiffpqQppppp",
@@ -122,45 +122,6 @@ def load():
 
 def available() -> bool:
     return torch.cuda.is_available() and _LIB_PATH.exists()
-
-
-# Optional second library: kernels that only a process driving one GPU with local operands may
-# use (cluster-multicast operand loads, csrc/cuda_single).  It is absent from installations that
-# are meant to run on several GPUs, and everything works without it.
-SINGLE_SIGS = {
-    "pcl_gemm_tf32_2sm_mc": "pppiiiqippppip",
-}
-_SINGLE = None
-_SINGLE_TRIED = False
-
-
-def load_single():
-    """The single-GPU kernel library, or None when it is not installed."""
-    global _SINGLE, _SINGLE_TRIED
-    if _SINGLE_TRIED:
-        return _SINGLE
-    _SINGLE_TRIED = True
-    path = _LIB_PATH.parent / "libpcl_kernels_single.so"
-    if path.exists() and os.environ.get("PCL_NO_SINGLE", "0") != "1":
-        lib = ctypes.CDLL(str(path))
-        for name, spec in SINGLE_SIGS.items():
-            fn = getattr(lib, name)
-            fn.argtypes = [_T[c] for c in spec]
-            fn.restype = ctypes.c_int
-        _SINGLE = lib
-    return _SINGLE
-
-
-def call_single(name: str, *args) -> None:
-    global _LAUNCHES
-    lib = load_single()
-    if lib is None:
-        raise KernelLibraryMissing("libpcl_kernels_single.so is not installed")
-    rc = getattr(lib, name)(*[_conv(a) for a in args])
-    _LAUNCHES += 1
-    if rc != 0:
-        msg = load().pcl_error_string(rc).decode()
-        raise RuntimeError(f"{name} failed: CUDA error {rc} ({msg})")
 
 
 def _conv(a):

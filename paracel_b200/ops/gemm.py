@@ -23,29 +23,19 @@ from . import _lib
 from ..parallel.symm import SymmBuffer
 
 
-# "2sm": pairs of CTAs on one 256 x 256 tile (tcgen05 cta_group::2, gemm_tf32_2sm.cu);
-# "1sm": one CTA per 128 x 128 tile (gemm_tf32.cu);
-# "2sm_mc": the pair kernel with clusters of four CTAs that share B through TMA multicast
-#   (csrc/cuda_single/gemm_tf32_2sm_mc.cu).  It exists only where the single-GPU kernel library is
-#   installed, takes local operands only, and is what ``gemm_nt`` / ``argmin_nt`` use by default
-#   in a process that is not part of a multi-rank job; otherwise they use "2sm".
-KERNEL = os.environ.get("PCL_GEMM_KERNEL", "auto")
-
-
-def _single_process() -> bool:
-    return not (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1)
+# "2sm": pairs of CTAs on one 256 x 256 (or 256 x 512) item (tcgen05 cta_group::2,
+#        gemm_tf32_2sm.cu);
+# "1sm": one CTA per 128 x 128 tile (gemm_tf32.cu).
+KERNEL = os.environ.get("PCL_GEMM_KERNEL", "2sm")
+# item form of the pair kernel: 1 = 256 x 512 (two accumulators share an A stage), 0 = 256 x 256
+# with alternating accumulators, -1 = the launcher chooses by K
+WIDE = int(os.environ.get("PCL_GEMM_WIDE", "-1"))
 
 
 def _entry(kernel: Optional[str] = None) -> str:
     k = kernel or KERNEL
-    if k == "auto":
-        k = "2sm_mc" if (_single_process() and _lib.load_single() is not None) else "2sm"
-    if k not in ("1sm", "2sm", "2sm_mc"):
+    if k not in ("1sm", "2sm"):
         raise ValueError(f"unknown GEMM kernel {k!r}")
-    if k == "2sm_mc":
-        if not _single_process():
-            raise ValueError("the multicast GEMM kernel is for single-GPU processes only")
-        return "pcl_gemm_tf32_2sm_mc"
     return "pcl_gemm_tf32_2sm" if k == "2sm" else "pcl_gemm_tf32"
 
 
@@ -99,23 +89,24 @@ def _merge_halves(rm2: torch.Tensor, ra2: torch.Tensor):
     return torch.where(take1, m1, m0), torch.where(take1, a1, a0)
 
 
-def _launch(A, B, C, epi, bnorm, row_min, row_arg, status=None, kernel=None):
+def _launch(A, B, C, epi, bnorm, row_min, row_arg, status=None, kernel=None, wide=None):
     M, K = A.shape
     if status is None:
         status = _status(A.device)
     N = B.shape[0]
     ldc = C.stride(0) if C is not None else 0
     entry = _entry(kernel)
-    if entry == "pcl_gemm_tf32_2sm_mc":
-        _lib.call_single(entry, A, B, C, M, N, K, ldc, epi, bnorm, row_min, row_arg, status, 0,
-                         _lib.stream_ptr())
+    if entry == "pcl_gemm_tf32_2sm":
+        _lib.call(entry, A, B, C, M, N, K, ldc, epi, bnorm, row_min, row_arg, None, None, 1, 0,
+                  N, 0, 0, status, 0, WIDE if wide is None else int(wide), _lib.stream_ptr())
         return
     _lib.call(entry, A, B, C, M, N, K, ldc, epi, bnorm, row_min, row_arg, None, None, 1, 0,
               N, 0, 0, status, 0, _lib.stream_ptr())
 
 
 def gemm_nt(A: torch.Tensor, B: torch.Tensor, out: Optional[torch.Tensor] = None,
-            precise: bool = False, kernel: Optional[str] = None) -> torch.Tensor:
+            precise: bool = False, kernel: Optional[str] = None,
+            wide: Optional[int] = None) -> torch.Tensor:
     _lib.check_cuda(A, torch.float32, "A")
     _lib.check_cuda(B, torch.float32, "B")
     assert A.shape[1] == B.shape[1]
@@ -126,12 +117,13 @@ def gemm_nt(A: torch.Tensor, B: torch.Tensor, out: Optional[torch.Tensor] = None
         A2, B2 = _pad_k(A), _pad_k(B)
     if out is None:
         out = torch.empty(M, N, device=A.device, dtype=torch.float32)
-    _launch(A2, B2, out, 0, None, None, None, kernel=kernel)
+    _launch(A2, B2, out, 0, None, None, None, kernel=kernel, wide=wide)
     return out
 
 
 def argmin_nt(A: torch.Tensor, B: torch.Tensor, bnorm: Optional[torch.Tensor] = None,
-              precise: bool = False, kernel: Optional[str] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+              precise: bool = False, kernel: Optional[str] = None,
+              wide: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """(min value of bnorm[n] - 2 a.b_n, its index n) per row of A."""
     _lib.check_cuda(A, torch.float32, "A")
     _lib.check_cuda(B, torch.float32, "B")
@@ -143,10 +135,10 @@ def argmin_nt(A: torch.Tensor, B: torch.Tensor, bnorm: Optional[torch.Tensor] = 
         A2, B2 = split3(_pad_k(A), False), split3(_pad_k(B), True)
     else:
         A2, B2 = _pad_k(A), _pad_k(B)
-    two = _entry(kernel) != "pcl_gemm_tf32"
+    two = _entry(kernel) == "pcl_gemm_tf32_2sm"
     row_min = torch.empty((2, M) if two else (M,), device=A.device, dtype=torch.float32)
     row_arg = torch.empty((2, M) if two else (M,), device=A.device, dtype=torch.int32)
-    _launch(A2, B2, None, 1, bnorm, row_min, row_arg, kernel=kernel)
+    _launch(A2, B2, None, 1, bnorm, row_min, row_arg, kernel=kernel, wide=wide)
     return _merge_halves(row_min, row_arg) if two else (row_min, row_arg)
 
 
@@ -159,7 +151,7 @@ class DenseReadGemm:
     """
 
     def __init__(self, N: int, K: int, group=None, device=None, gather_ctas: int = 8,
-                 kernel: Optional[str] = None):
+                 kernel: Optional[str] = None, wide: Optional[int] = None):
         if K % 4:
             raise ValueError("K must be a multiple of 4")
         self.N, self.K = N, K
@@ -175,9 +167,15 @@ class DenseReadGemm:
         self.status = torch.zeros(4, dtype=torch.int64, device=self.device)
         self.epoch = 0
         self.gather_ctas = gather_ctas
-        k = kernel or KERNEL
-        # the shards may be peers' memory: never the multicast kernel here
-        self.entry = _entry("2sm" if k in ("auto", "2sm_mc") else k)
+        self.entry = _entry(kernel)
+        self.wide = WIDE if wide is None else int(wide)
+
+    @property
+    def _tail(self):
+        # trailing launcher arguments: the pair kernel takes its tile form before the stream
+        if self.entry == "pcl_gemm_tf32_2sm":
+            return (self.wide, _lib.stream_ptr())
+        return (_lib.stream_ptr(),)
 
     def local_rows(self) -> Tuple[int, int]:
         lo = self.rank * self.rps
@@ -198,14 +196,14 @@ class DenseReadGemm:
                 out = torch.empty(M, self.N, device=A.device, dtype=torch.float32)
             _lib.call(self.entry, A, stage, out, M, self.N, self.K, out.stride(0), 0, None, None,
                       None, shards, self.flags, self.world, self.rank, self.rps, self.epoch,
-                      self.gather_ctas, self.status, 0, _lib.stream_ptr())
+                      self.gather_ctas, self.status, 0, *self._tail)
             return out
         two = self.entry == "pcl_gemm_tf32_2sm"
         row_min = torch.empty((2, M) if two else (M,), device=A.device, dtype=torch.float32)
         row_arg = torch.empty((2, M) if two else (M,), device=A.device, dtype=torch.int32)
         _lib.call(self.entry, A, stage, None, M, self.N, self.K, 0, 1, argmin_bnorm, row_min,
                   row_arg, shards, self.flags, self.world, self.rank, self.rps, self.epoch,
-                  self.gather_ctas, self.status, 0, _lib.stream_ptr())
+                  self.gather_ctas, self.status, 0, *self._tail)
         return _merge_halves(row_min, row_arg) if two else (row_min, row_arg)
 
     def check(self):

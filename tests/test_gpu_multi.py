@@ -52,7 +52,7 @@ def test_mf_two_ranks_converges_like_one_rank():
 
 
 @needs2
-@pytest.mark.parametrize("kernel", ["1sm", "2sm"])
+@pytest.mark.parametrize("kernel", ["1sm", "2sm", "2sm-wide"])
 def test_fused_allgather_gemm_two_ranks(kernel):
     from workers.gpu_workers import fused_gather_gemm
     res = _job(2).run(fused_gather_gemm, (1000, 64, 900, kernel), timeout_s=300)

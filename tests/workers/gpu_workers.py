@@ -142,7 +142,10 @@ def fused_gather_gemm(comm, server_info, N, K, M, kernel=None):
     Bfull = torch.randn(N, K, device=dev, generator=g)        # same on every rank
     g.manual_seed(1000 + rank)
     A = torch.randn(M, K, device=dev, generator=g)
-    op = DenseReadGemm(N, K, kernel=kernel)
+    if kernel == "2sm-wide":        # 256 x 512 items of the pair kernel
+        op = DenseReadGemm(N, K, kernel="2sm", wide=1)
+    else:
+        op = DenseReadGemm(N, K, kernel=kernel, wide=0)
     lo, hi = op.local_rows()
     op.shard[: hi - lo] = Bfull[lo:hi]
     torch.cuda.synchronize()
