@@ -118,6 +118,21 @@ def grid_rank(u: torch.Tensor, i: torch.Tensor, ugrp: torch.Tensor, igrp: torch.
     return gu * npy + gi
 
 
+class RoundResult:
+    """Result of one ``round()``: the squared pre-update error of its SGD pass.  The 8-byte copy
+    to pinned host memory is queued right behind the pass, so ``sse()`` waits for that copy only
+    and a caller that keeps one round in flight (queue round t + 1, then read round t) never lets
+    the device run dry while the host reads."""
+    __slots__ = ("_ev", "_host")
+
+    def __init__(self, ev, host):
+        self._ev, self._host = ev, host
+
+    def sse(self) -> float:
+        self._ev.synchronize()
+        return float(self._host.item())
+
+
 class MfSgdGpu(paralg):
     def __init__(self, n_users: int, n_items: int, k: int = 128, alpha: float = 0.005,
                  beta: float = 0.02, rounds: int = 1, staleness: int = 2, ssp: bool = True,
@@ -126,7 +141,7 @@ class MfSgdGpu(paralg):
                  chunks_per_flush: int = 8, variant: int = 0, compact: bool = True,
                  comm=None, hosts_dct_str=None, output: str = "", user_names=None,
                  item_names=None, update_funcs=None, flush_scale: float = 0.0,
-                 flush_mode: str = "uniform", grid=None):
+                 flush_mode: str = "uniform", grid=None, stream_segments: Optional[int] = None):
         super().__init__(hosts_dct_str, comm, output, int(rounds), int(staleness) if ssp else 0,
                          bool(ssp), wait_timeout_s=timeout_s, backend="gpu", device=device,
                          group=group)
@@ -199,7 +214,18 @@ class MfSgdGpu(paralg):
         self.but, self.bit = self.ub_tab.table, self.ib_tab.table
         self.mu = 0.0
         self.nnz = 0
+        # Segments per round when the ratings are streamed from host memory (offload_ratings);
+        # None: one per 64 M local ratings, at least 2 and at most 8.  Every segment is a kernel
+        # launch with its own replica set-up and tail (about 60 us): measured on 200 M ratings,
+        # 2 / 4 / 8 / 16 segments cost 0.1 / 0.25 / 0.5 / 1.4 ms on a 28.4 ms round.
+        env_seg = os.environ.get("PCL_MF_STREAM_SEGMENTS")
+        self.stream_segments = (int(stream_segments) if stream_segments is not None
+                                else int(env_seg) if env_seg else None)
         self.sse = torch.zeros(1, dtype=torch.float64, device=self.device)
+        # results of the last four rounds in pinned host memory (see RoundResult)
+        self._sse_host = torch.zeros(4, 1, dtype=torch.float64).pin_memory()
+        self._sse_ev = [torch.cuda.Event() for _ in range(4)]
+        self._res_no = 0
         self.host_stream = None
         self.h2d_bytes = 0
         self._loaded = False
@@ -460,9 +486,12 @@ class MfSgdGpu(paralg):
                       self.sgd_blocks, self.sse, self.variant, pk, self.chdr if pk is not None else None,
                       self.rtable if pk is not None else None, s)
         else:
-            self._sgd_pass_streamed()
+            nseg = self.stream_segments
+            if nseg is None:
+                nseg = max(2, min(8, round(self.h_ru.numel() / 64e6)))
+            self._sgd_pass_streamed(nseg)
 
-    def _sgd_pass_streamed(self, nseg: int = 16):
+    def _sgd_pass_streamed(self, nseg: int):
         """Out-of-core pass: ratings come from pinned host memory in segments; the copy of
         segment s+1 overlaps the SGD kernel of segment s (two staging buffers), and the copy of
         the NEXT round's first segment is queued as soon as this round's last kernel is, so it
@@ -617,7 +646,10 @@ class MfSgdGpu(paralg):
             self._push_done = torch.cuda.Event()
             self._push_done.record(self._push_stream)
 
-    def round(self):
+    def round(self) -> RoundResult:
+        """One round: pull (or wait for) the rows, one SGD pass over the local ratings, push, commit.
+        Everything is queued on the current stream; the returned handle gives the pass's squared
+        error once its copy has arrived."""
         with self.phase("pull_or_wait"):
             if self._push_done is not None and self.paracel_would_pull(self.kW, self.Wl):
                 # the pull must see this rank's own pushes
@@ -626,6 +658,11 @@ class MfSgdGpu(paralg):
         with self.phase("sgd"):
             self.sse.zero_()
             self.sgd_pass()
+        slot = self._res_no % 4
+        self._res_no += 1
+        self._sse_host[slot].copy_(self.sse, non_blocking=True)
+        self._sse_ev[slot].record()
+        result = RoundResult(self._sse_ev[slot], self._sse_host[slot])
         if self.overlap_push and self.world > 1 and self.ssp and self.staleness >= 2:
             self._push_overlapped()
         else:
@@ -635,7 +672,8 @@ class MfSgdGpu(paralg):
             self.log_metrics(round=self.clock, ratings=self.nnz, rows_held=rows,
                              bytes_pulled=rows * (self.D + 1) * 4, bytes_pushed=rows * (self.D + 1) * 4,
                              h2d_bytes=self.h2d_bytes, staleness=self.staleness,
-                             sse_of_pass=float(self.sse.item()) if self.metrics_sync else None)
+                             sse_of_pass=result.sse() if self.metrics_sync else None)
+        return result
 
     def phase_times_ms(self):
         """Mean device time of each phase of round() over the rounds run since ``phase_timing``
