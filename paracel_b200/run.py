@@ -133,6 +133,17 @@ def _wc(comm, info, pt):
     return s
 
 
+def _ssi(comm, info, pt):
+    """Steady-state inversion, parallel over the left nodes (the reference has the serial tool only;
+    same config keys as that tool: bigraph_input, distribution_input, output)."""
+    from .models.ssi import steady_state_inversion
+    s = steady_state_inversion(comm, info, pt.check_parse("bigraph_input", str), pt.get("output", ""),
+                               pt.check_parse("distribution_input", str))
+    s.solve()
+    s.dump_result()
+    return s
+
+
 def _sim_dense(comm, info, pt):
     from .models.similarity import sim_dense
     a = pt.get("input") or pt.get("input_a")
@@ -198,6 +209,7 @@ ALGORITHMS: Dict[str, Callable] = {
     "lda": _lda, "kmeans": _kmeans, "pagerank": _pagerank, "mvv": _mvv, "wc": _wc,
     "sim_dense": _sim_dense, "ab_sim_dense": _sim_dense, "sim_sparse": _sim_sparse,
     "adjust_ktop_sparse": _adjust_ktop, "dtr": _dtr, "lr_l1": _l1, "lasso": _lasso,
+    "steady_state_inversion": _ssi,
 }
 
 

@@ -83,6 +83,59 @@ def test_svd_two_workers_matches_numpy(tmp_path):
     assert np.allclose(res[0]["sigma"], ref, rtol=1e-6)
     sig = [float(x) for x in open(str(tmp_path / "o" / "SIGMA_0")).read().strip().split(",")]
     assert np.allclose(sig, ref, rtol=1e-5)
+    # the serial tool (numpy only, no code shared with the parallel class) as oracle: same
+    # singular values and, up to the sign of a column, the same left singular vectors per row id
+    from paracel_b200.tool import svd_serial
+    ser = svd_serial.solve(str(tmp_path / "a.csv"), str(tmp_path / "os"), 3, iters=15)
+    assert np.allclose(ser.sigma, res[0]["sigma"], rtol=1e-6)
+    from paracel_b200.utils.dump import files_merge, read_dict_vector
+    files_merge(str(tmp_path / "o" / "U_*"), str(tmp_path / "U_par"))
+    Up, Us = read_dict_vector(str(tmp_path / "U_par")), read_dict_vector(str(tmp_path / "os" / "U_0"))
+    assert sorted(Up) == sorted(Us) and len(Up) == 30
+    P = np.array([Up[r] for r in sorted(Up)], dtype=float)
+    S = np.array([Us[r] for r in sorted(Up)], dtype=float)
+    for c in range(3):
+        assert min(np.abs(P[:, c] - S[:, c]).max(), np.abs(P[:, c] + S[:, c]).max()) < 1e-5
+
+
+def test_steady_state_inversion_two_workers_matches_serial_tool(tmp_path):
+    """The parallel class against the serial tool on a random bipartite graph whose target
+    distribution is far from what the initial scores deliver."""
+    from paracel_b200.tool.steady_state_inversion_serial import steady_state_inversion as serial
+    from paracel_b200.utils.dump import files_merge
+    rng = np.random.default_rng(5)
+    nl, nr = 40, 12
+    lines = []
+    for i in range(nl):
+        for j in rng.choice(nr, size=4, replace=False):
+            lines.append(f"n{i}L,m{j}R,{rng.uniform(0.5, 3.0):.6f}\n")
+    (tmp_path / "bg.csv").write_text("".join(lines))
+    pl = rng.dirichlet(np.ones(nl))
+    pr = rng.dirichlet(np.ones(nr) * 3.0)
+    (tmp_path / "dis.csv").write_text("".join(f"n{i}L,{pl[i]:.10f}\n" for i in range(nl)) +
+                                      "".join(f"m{j}R,{pr[j]:.10f}\n" for j in range(nr)))
+    ser = serial(str(tmp_path / "bg.csv"), str(tmp_path / "dis.csv"), str(tmp_path / "os"))
+    ser.solve()
+    ser.dump_result()
+    res = LocalJob(2, 1).run(W.run_ssi, (str(tmp_path / "bg.csv"), str(tmp_path / "dis.csv"), str(tmp_path / "op")),
+                             timeout_s=300)
+    assert res[0]["left"] + res[1]["left"] == nl and res[0]["left"] > 0 and res[1]["left"] > 0
+    assert res[0]["score"] == res[1]["score"]
+    for r, v in ser.score_new.items():
+        assert abs(res[0]["score"][r] - v) <= 1e-8 * max(1.0, abs(v)), (r, v, res[0]["score"][r])
+    # the scores moved, and the dumps agree line by line after merging the workers' parts
+    assert any(abs(ser.score_new[f"m{j}R"] - pr[j]) > 1e-6 for j in range(nr))
+    files_merge(str(tmp_path / "op" / "transfer_prob_matrix_*"), str(tmp_path / "tp_par"))
+    par = sorted(open(str(tmp_path / "tp_par")).read().strip().split("\n"))
+    one = sorted(open(str(tmp_path / "os" / "transfer_prob_matrix_0")).read().strip().split("\n"))
+    assert len(par) == len(one) == nl
+    for a, b in zip(par, one):
+        ka, kb = a.split("\t")[0], b.split("\t")[0]
+        assert ka == kb
+        ea = dict(x.split(":") for x in a.split("\t")[1].split("|"))
+        eb = dict(x.split(":") for x in b.split("\t")[1].split("|"))
+        assert ea.keys() == eb.keys()
+        assert all(abs(float(ea[k]) - float(eb[k])) < 1e-6 for k in ea)
 
 
 def test_serial_tools(tmp_path):

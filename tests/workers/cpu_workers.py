@@ -290,6 +290,16 @@ def run_svd(comm, server_info, inp, out, k):
     return {"sigma": m.sigma.tolist()}
 
 
+def run_ssi(comm, server_info, graph, dis, out):
+    from paracel_b200.models.ssi import steady_state_inversion
+    m = steady_state_inversion(comm, server_info, graph, out, dis)
+    m.solve()
+    m.dump_result()
+    res = {"score": dict(zip(m.right, m.score.tolist())), "sweeps": m.sweeps, "left": len(m.left)}
+    m.close()
+    return res
+
+
 def checkpoint_resume(comm, server_info, inp, ckpt, phase):
     """LR (dgd, deterministic) for 6 rounds at once, or 3 rounds + checkpoint, or resume + 3."""
     import numpy as np
