@@ -162,40 +162,98 @@ struct SparseGradArgs {
 // most warps of a CTA at once).  |residual * value| <= a few units and a CTA adds at most a
 // few hundred thousand terms per feature, so 17 integer bits are ample.
 constexpr float SG_FX = 16384.f, SG_FXI = 1.f / 16384.f;
+#ifndef SG_ROWS_N
+#define SG_ROWS_N 4
+#endif
+constexpr int SG_ROWS = SG_ROWS_N;
 
+// residual of one row from its margin z; adds the row's loss
+__device__ __forceinline__ float sg_residual(const SparseGradArgs& a, float z, float yy, double& loss) {
+  if (a.logistic) {
+    const float h = sigmoidf_(z);
+    const float hc = fminf(fmaxf(h, 1e-7f), 1.f - 1e-7f);
+    loss += (yy == 1.f) ? -(double)__logf(hc) : -(double)__logf(1.f - hc);
+    return yy - h;
+  }
+  const float r = yy - z;
+  loss += (double)r * (double)r;
+  return r;
+}
+
+__device__ __forceinline__ void sg_scatter(const SparseGradArgs& a, int* s_hot, int c, float t, bool fx_ok) {
+  if (c < a.hot_T && fx_ok && fabsf(t) < 64.f) atomicAdd(&s_hot[c], __float2int_rn(t * SG_FX));
+  else atomicAdd(a.g + c, t);
+}
+
+// A warp takes SG_ROWS rows per step.  A row is a chain of dependent long-latency accesses (row
+// pointers, column ids, gather of theta, then the atomics), and with one row per warp the SM had
+// only as many chains in flight as resident warps (long scoreboard 17 stall cycles per issue).
+// Rows of up to 64 non-zeros keep their ids and values in registers between the margin and the
+// scatter; longer rows take the loop form.
 __global__ void __launch_bounds__(256) sparse_grad_kernel(SparseGradArgs a) {
   extern __shared__ int s_hot[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
   for (int j = threadIdx.x; j < a.hot_T; j += blockDim.x) s_hot[j] = 0;
   __syncthreads();
   double loss = 0.0;
-  for (long long row = (long long)blockIdx.x * wpb + warp; row < a.n; row += (long long)gridDim.x * wpb) {
-    const long long b = a.row_ptr[row], e = a.row_ptr[row + 1];
-    float z = 0.f;
-    for (long long p = b + lane; p < e; p += 32) {
-      const float v = a.vals ? a.vals[p] : 1.f;
-      z = fmaf(v, __ldg(a.theta + a.cols[p]), z);
+  // squared-loss residuals are unbounded: keep those in floating point
+  const bool fx_ok = a.logistic != 0;
+  const long long stride = (long long)gridDim.x * wpb;
+  for (long long row0 = (long long)blockIdx.x * wpb + warp; row0 < a.n; row0 += SG_ROWS * stride) {
+    long long rb[SG_ROWS], re[SG_ROWS];
+    bool shortrows = true;
+#pragma unroll
+    for (int k = 0; k < SG_ROWS; ++k) {
+      const long long row = row0 + k * stride;
+      const bool has = row < a.n;
+      rb[k] = has ? a.row_ptr[row] : 0;
+      re[k] = has ? a.row_ptr[row + 1] : 0;
+      shortrows &= (re[k] - rb[k] <= 64);
     }
-    z = pcl_warp_sum(z);
-    const float yy = a.y[row];
-    float r;
-    if (a.logistic) {
-      const float h = sigmoidf_(z);
-      r = yy - h;
-      const float hc = fminf(fmaxf(h, 1e-7f), 1.f - 1e-7f);
-      loss += (yy == 1.f) ? -(double)__logf(hc) : -(double)__logf(1.f - hc);
-    } else {
-      r = yy - z;
-      loss += (double)r * (double)r;
+    if (shortrows) {
+      // ids and values of all rows, then all gathers, then the reductions
+      int c[2 * SG_ROWS];
+      float v[2 * SG_ROWS], t[2 * SG_ROWS];
+#pragma unroll
+      for (int q = 0; q < 2 * SG_ROWS; ++q) {
+        const long long p = rb[q >> 1] + (q & 1) * 32 + lane;
+        const bool in = p < re[q >> 1];
+        c[q] = in ? __ldg(a.cols + p) : -1;
+        v[q] = (in && a.vals) ? __ldg(a.vals + p) : 1.f;
+      }
+#pragma unroll
+      for (int q = 0; q < 2 * SG_ROWS; ++q) t[q] = c[q] >= 0 ? __ldg(a.theta + c[q]) : 0.f;
+      float z[SG_ROWS];
+#pragma unroll
+      for (int k = 0; k < SG_ROWS; ++k) z[k] = fmaf(v[2 * k], t[2 * k], v[2 * k + 1] * t[2 * k + 1]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int k = 0; k < SG_ROWS; ++k) z[k] += __shfl_xor_sync(0xffffffffu, z[k], o);
+#pragma unroll
+      for (int k = 0; k < SG_ROWS; ++k) {
+        const long long row = row0 + k * stride;
+        if (row >= a.n) break;
+        const float r = sg_residual(a, z[k], a.y[row], loss);
+        if (c[2 * k] >= 0) sg_scatter(a, s_hot, c[2 * k], r * v[2 * k], fx_ok);
+        if (c[2 * k + 1] >= 0) sg_scatter(a, s_hot, c[2 * k + 1], r * v[2 * k + 1], fx_ok);
+      }
+      continue;
     }
-    // squared-loss residuals are unbounded: keep those in floating point
-    const bool fx_ok = a.logistic != 0;
-    for (long long p = b + lane; p < e; p += 32) {
-      const int c = a.cols[p];
-      const float v = a.vals ? a.vals[p] : 1.f;
-      const float t = r * v;
-      if (c < a.hot_T && fx_ok && fabsf(t) < 64.f) atomicAdd(&s_hot[c], __float2int_rn(t * SG_FX));
-      else atomicAdd(a.g + c, t);
+    for (int k = 0; k < SG_ROWS; ++k) {
+      const long long row = row0 + k * stride;
+      if (row >= a.n) break;
+      float zz = 0.f;
+      for (long long q = rb[k] + lane; q < re[k]; q += 32) {
+        const float vv = a.vals ? a.vals[q] : 1.f;
+        zz = fmaf(vv, __ldg(a.theta + a.cols[q]), zz);
+      }
+      zz = pcl_warp_sum(zz);
+      const float r = sg_residual(a, zz, a.y[row], loss);
+      for (long long q = rb[k] + lane; q < re[k]; q += 32) {
+        const float vv = a.vals ? a.vals[q] : 1.f;
+        sg_scatter(a, s_hot, a.cols[q], r * vv, fx_ok);
+      }
     }
   }
   __syncthreads();
