@@ -21,6 +21,8 @@
 // Kept: 1 / (n_k + V beta) in shared memory instead of registers (128 -> 95 registers, 16 -> 20
 // warps per SM, 1.32 G -> 1.41 G tokens/s).  Parking the lane's running sums there as well (80
 // registers, 24 warps, 32 KB of shared memory per block) was slower again: 1.36 G.
+// Also measured and not kept: a prefetch.global.L2 of the next token's row (no registers held):
+// 1.26 G tokens/s against 1.41 G.
 #include "common.cuh"
 
 namespace {
