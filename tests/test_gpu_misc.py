@@ -57,6 +57,24 @@ def test_kmeans_gpu_matches_numpy_lloyd():
     m.free()
 
 
+@pytest.mark.parametrize("n,d,k", [(5003, 128, 37), (4001, 64, 5), (3000, 256, 100), (2500, 512, 9),
+                                   (3001, 10, 7), (2000, 516, 3), (3, 128, 2)])
+def test_kmeans_accumulate_matches_index_add(n, d, k):
+    """Per-cluster sums and counts (vector-reduction kernel for d % 4 == 0 and d <= 512, the scalar
+    kernel otherwise) against a plain fp64 index_add."""
+    from paracel_b200.ops.misc import kmeans_accumulate
+    g = torch.Generator(device="cuda").manual_seed(n + d)
+    X = torch.randn(n, d, device="cuda", generator=g)
+    assign = torch.randint(0, k, (n,), device="cuda", generator=g, dtype=torch.int32)
+    sums = torch.zeros(k, d, device="cuda")
+    counts = torch.zeros(k, device="cuda")
+    kmeans_accumulate(X, assign, sums, counts)
+    ref = torch.zeros(k, d, device="cuda", dtype=torch.float64).index_add_(0, assign.long(), X.double())
+    cnt = torch.bincount(assign.long(), minlength=k).double()
+    assert torch.equal(counts.double(), cnt)
+    assert (sums.double() - ref).abs().max().item() < 1e-3
+
+
 def test_running_topk_and_gram():
     from paracel_b200.ops.misc import RunningTopK, gram
     dev = "cuda:0"
