@@ -41,36 +41,36 @@ __global__ void __launch_bounds__(256) dense_read_kernel(ReadArgs a) {
     __syncthreads();
     if (!ok) return;
   }
-  const long long nvec = a.L >> 2;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nth = (long long)gridDim.x * blockDim.x;
-  // Ring order: rank r starts with its own shard and walks r+1, r+2, ...; at any moment the
-  // ranks read from different owners instead of all from shard 0.  Four loads in flight per thread.
-  const long long shift = ((long long)a.rank * a.S) >> 2;   // S is a multiple of 4
-  for (long long v0 = tid; v0 < nvec; v0 += 4 * nth) {
-    float4 x[4];
-    long long e[4];
+  // Ring order: rank r copies its own shard first, then r + 1, r + 2, ...; at any moment the ranks
+  // read from different owners instead of all from shard 0.  One loop per shard (no division to
+  // find an element's owner), eight 16-byte loads in flight per thread.
+  constexpr int U = 4;
+  for (int k = 0; k < a.world; ++k) {
+    int o = a.rank + k;
+    if (o >= a.world) o -= a.world;
+    const long long base = (long long)o * a.S;
+    // the last shard takes whatever is left of L
+    const long long len = (o == a.world - 1) ? a.L - base : (a.S < a.L - base ? a.S : a.L - base);
+    if (len <= 0) continue;
+    const float* src = a.shards[o];
+    float* dst = a.out + base;
+    const long long nv = len >> 2;
+    for (long long v0 = tid; v0 < nv; v0 += U * nth) {
+      float4 x[U];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const long long v = v0 + u * nth;
-      e[u] = -1;
-      if (v < nvec) {
-        long long vv = v + shift;
-        if (vv >= nvec) vv -= nvec;
-        e[u] = vv << 2;
-        int owner = (int)(e[u] / a.S);
-        if (owner >= a.world) owner = a.world - 1;
-        x[u] = pcl_ld_sys4(a.shards[owner] + (e[u] - (long long)owner * a.S));
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * nth;
+        if (v < nv) x[u] = pcl_ld_sys4(src + (v << 2));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * nth;
+        if (v < nv) *reinterpret_cast<float4*>(dst + (v << 2)) = x[u];
       }
     }
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-      if (e[u] >= 0) *reinterpret_cast<float4*>(a.out + e[u]) = x[u];
-  }
-  for (long long e = (nvec << 2) + tid; e < a.L; e += nth) {
-    int owner = (int)(e / a.S);
-    if (owner >= a.world) owner = a.world - 1;
-    a.out[e] = a.shards[owner][e - (long long)owner * a.S];
+    for (long long e = (nv << 2) + tid; e < len; e += nth) dst[e] = src[e];
   }
 }
 
@@ -104,6 +104,10 @@ __device__ __forceinline__ float apply_handler(int handler, float th, float sum,
   }
 }
 
+// IS_MAX: the max handler keeps a running maximum of the deltas, every other handler their sum;
+// the two forms are separate instances so that neither carries the other's registers.  Four
+// 16-byte columns per thread: eight need 176 registers and were a quarter slower.
+template <bool IS_MAX>
 __global__ void __launch_bounds__(256) dense_bupdate_kernel(BupArgs a) {
   __shared__ int ok;
   if (a.ready != nullptr && a.epoch > 0) {
@@ -123,43 +127,46 @@ __global__ void __launch_bounds__(256) dense_bupdate_kernel(BupArgs a) {
   const bool vec_ok = ((lo & 3) == 0);
   const long long nvec = vec_ok ? (n >> 2) : 0;
   float nz = 0.f;
-  // four independent 16-byte columns per thread and trip: all their loads (the shard and every
+  // U independent 16-byte columns per thread and trip: all their loads (the shard and every
   // rank's delta) are issued before the first handler is applied
-  for (long long v0 = tid; v0 < nvec; v0 += 4 * nth) {
-    float4 s[4], m[4], t[4];
+  constexpr int U = 2;
+  for (long long v0 = tid; v0 < nvec; v0 += U * nth) {
+    float4 s[U], t[U];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < U; ++u) {
       const long long v = v0 + u * nth;
-      s[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      m[u] = make_float4(-3.4e38f, -3.4e38f, -3.4e38f, -3.4e38f);
+      s[u] = IS_MAX ? make_float4(-3.4e38f, -3.4e38f, -3.4e38f, -3.4e38f) : make_float4(0.f, 0.f, 0.f, 0.f);
       if (v < nvec) t[u] = *reinterpret_cast<const float4*>(a.theta + (v << 2));
     }
     for (int i = 0; i < a.world; ++i) {
       int r = a.rank + i;
       if (r >= a.world) r -= a.world;
-      float4 d[4];
+      float4 d[U];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         const long long v = v0 + u * nth;
         if (v < nvec) d[u] = pcl_ld_sys4(a.deltas[r] + lo + (v << 2));
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         if (v0 + u * nth >= nvec) continue;
-        s[u].x += d[u].x; s[u].y += d[u].y; s[u].z += d[u].z; s[u].w += d[u].w;
-        m[u].x = fmaxf(m[u].x, d[u].x); m[u].y = fmaxf(m[u].y, d[u].y);
-        m[u].z = fmaxf(m[u].z, d[u].z); m[u].w = fmaxf(m[u].w, d[u].w);
+        if (IS_MAX) {
+          s[u].x = fmaxf(s[u].x, d[u].x); s[u].y = fmaxf(s[u].y, d[u].y);
+          s[u].z = fmaxf(s[u].z, d[u].z); s[u].w = fmaxf(s[u].w, d[u].w);
+        } else {
+          s[u].x += d[u].x; s[u].y += d[u].y; s[u].z += d[u].z; s[u].w += d[u].w;
+        }
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < U; ++u) {
       const long long v = v0 + u * nth;
       if (v >= nvec) continue;
       float4 x = t[u];
-      x.x = apply_handler(a.handler, x.x, s[u].x, m[u].x, a.lr, a.lambda);
-      x.y = apply_handler(a.handler, x.y, s[u].y, m[u].y, a.lr, a.lambda);
-      x.z = apply_handler(a.handler, x.z, s[u].z, m[u].z, a.lr, a.lambda);
-      x.w = apply_handler(a.handler, x.w, s[u].w, m[u].w, a.lr, a.lambda);
+      x.x = apply_handler(a.handler, x.x, s[u].x, s[u].x, a.lr, a.lambda);
+      x.y = apply_handler(a.handler, x.y, s[u].y, s[u].y, a.lr, a.lambda);
+      x.z = apply_handler(a.handler, x.z, s[u].z, s[u].z, a.lr, a.lambda);
+      x.w = apply_handler(a.handler, x.w, s[u].w, s[u].w, a.lr, a.lambda);
       *reinterpret_cast<float4*>(a.theta + (v << 2)) = x;
       nz += (x.x != 0.f) + (x.y != 0.f) + (x.z != 0.f) + (x.w != 0.f);
     }
@@ -253,7 +260,7 @@ PCL_API int pcl_dense_read(const float* const* shards, float* out, long long L, 
   ReadArgs a{shards, out, L, S, world, rank, flags, target, timeout_ns, status};
   long long blocks = (L / 4 + 255) / 256;
   if (blocks < 1) blocks = 1;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
   dense_read_kernel<<<(int)blocks, 256, 0, stream>>>(a);
   return pcl_last_error();
 }
@@ -268,8 +275,9 @@ PCL_API int pcl_dense_bupdate(float* theta, const float* const* deltas, long lon
             status, done_ptrs, block_counter, nnz_out};
   long long blocks = (S / 4 + 255) / 256;
   if (blocks < 1) blocks = 1;
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  dense_bupdate_kernel<<<(int)blocks, 256, 0, stream>>>(a);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (handler == DH_MAX) dense_bupdate_kernel<true><<<(int)blocks, 256, 0, stream>>>(a);
+  else dense_bupdate_kernel<false><<<(int)blocks, 256, 0, stream>>>(a);
   return pcl_last_error();
 }
 
