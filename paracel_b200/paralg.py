@@ -690,7 +690,7 @@ class paralg:
 
     def paracel_read_special(self, file_name: str = "", func_name: str = "") -> Dict[str, Any]:
         """Every parameter whose key passes the filter: host shards and device tables alike (a
-        device table is selected as a whole by the filter's verdict on its key pattern)."""
+        device table is selected as a whole by the filter's answer for its key pattern)."""
         d: Dict[str, Any] = {}
         if self.ps_obj is not None:
             for c in self.ps_obj.kvm:
