@@ -11,6 +11,11 @@
 // The pull kernel can also carry the SSP staleness wait (bounded spin on the
 // clock words that peers store into this GPU's memory), so that "wait until
 // nobody is more than s clocks behind, then read" is one launch.
+//
+// Measured and not kept: four rows in flight per lane group in the pull and two in the push (ids of
+// all rows, then all loads, then the stores / reductions) with 32-bit owner arithmetic.  On one
+// GPU the pull went from 0.56 to 0.61 ms and the push from 0.70 to 0.84 ms for two million rows of
+// 512 bytes: one row per group with 64 resident warps per SM already keeps the memory system busy.
 #include "common.cuh"
 
 namespace {

@@ -75,6 +75,50 @@ def test_kmeans_accumulate_matches_index_add(n, d, k):
     assert (sums.double() - ref).abs().max().item() < 1e-3
 
 
+@pytest.mark.parametrize("rows,width,n", [(1000, 128, 3001), (77, 4, 5), (5000, 64, 2500), (300, 200, 1237),
+                                          (4096, 512, 700)])
+def test_row_table_pull_push_match_torch(rows, width, n):
+    """Keyed pull (with snapshot) and the add / scaled_add / max / assign pushes of a row table
+    against plain PyTorch indexing in fp64; ids repeat, so pushes to one row accumulate."""
+    from paracel_b200.ps.tables import RowTable
+    g = torch.Generator(device="cuda").manual_seed(rows + width)
+    t = RowTable(rows, width)
+    ref = torch.randn(rows, width, device="cuda", generator=g)
+    t.shard[:rows] = ref
+    ids = torch.randint(0, rows, (n,), device="cuda", generator=g)
+    out = torch.empty(n, width, device="cuda")
+    snap = torch.empty(n, width, device="cuda")
+    t.pull(ids, out, snap)
+    t.check()
+    assert torch.equal(out, ref[ids]) and torch.equal(snap, ref[ids])
+    # add with per-row weights: table += w * (cur - old); old is refreshed to cur
+    cur = out + torch.randn(n, width, device="cuda", generator=g)
+    w = torch.rand(n, device="cuda", generator=g)
+    exp = ref.double().index_add_(0, ids, (cur - snap).double() * w.double()[:, None])
+    t.push(ids, cur, snap, w, handler="add", start=n // 3)
+    t.check()
+    assert (t.shard[:rows].double() - exp).abs().max().item() < 1e-4
+    assert torch.equal(snap, cur)
+    # scaled add without snapshot: table += scale * cur
+    exp = t.shard[:rows].double().index_add_(0, ids, 0.25 * cur.double())
+    t.push(ids, cur, None, None, handler="scaled_add", scale=0.25)
+    t.check()
+    assert (t.shard[:rows].double() - exp).abs().max().item() < 1e-4
+    # max
+    before = t.shard[:rows].clone()
+    exp = before.clone().index_reduce_(0, ids, cur, "amax", include_self=True)
+    t.push(ids, cur, None, None, handler="max")
+    t.check()
+    assert torch.equal(t.shard[:rows], exp)
+    # assign on distinct ids
+    uids = torch.randperm(rows, device="cuda", generator=g)[: min(rows, n)]
+    vals = torch.randn(uids.numel(), width, device="cuda", generator=g)
+    t.push(uids, vals, None, None, handler="assign")
+    t.check()
+    assert torch.equal(t.shard[:rows][uids], vals)
+    t.free()
+
+
 def test_running_topk_and_gram():
     from paracel_b200.ops.misc import RunningTopK, gram
     dev = "cuda:0"
