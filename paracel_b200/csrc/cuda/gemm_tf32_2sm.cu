@@ -37,6 +37,10 @@
 // (slower on every shape), coalesced 128-bit global stores out of the staging buffer (8 % slower),
 // 256-bit stores straight from the registers (17 % slower), L2 evict-first / evict-last hints on
 // the C stores and the B loads (within 2 %), a start-up stagger between the pairs (no change).
+// Measured and not kept for the main loop: stages of 16 elements of K (64-byte rows, 64-byte
+// swizzle, twelve or eight stages instead of six or four, so that a larger share of the operand
+// memory is in flight): numerically identical, but 428 against 583 TFLOP/s at 65536 x 16384 x 512 and
+// 555 against 701 at 8192^3; the copy engine and L2 do worse on half-line rows than the deeper ring gains.
 // Every wait has a time limit; on expiry the status record is written, both
 // CTAs of the pair are told to leave, tensor memory is freed and the kernel ends.
 #include <cuda.h>
