@@ -215,9 +215,9 @@ class MfSgdGpu(paralg):
         self.mu = 0.0
         self.nnz = 0
         # Segments per round when the ratings are streamed from host memory (offload_ratings);
-        # None: one per 64 M local ratings, at least 2 and at most 8.  Every segment is a kernel
-        # launch with its own replica set-up and tail (about 60 us): measured on 200 M ratings,
-        # 2 / 4 / 8 / 16 segments cost 0.1 / 0.25 / 0.5 / 1.4 ms on a 28.4 ms round.
+        # None: as many as keep a staging buffer within 1 GiB, at least 2.  Every segment is a
+        # kernel launch with its own replica set-up and tail (about 60 us): measured on 200 M
+        # ratings (675 MB), 2 / 4 / 8 / 16 segments cost 0.1 / 0.25 / 0.5 / 1.4 ms on a 28.4 ms round.
         env_seg = os.environ.get("PCL_MF_STREAM_SEGMENTS")
         self.stream_segments = (int(stream_segments) if stream_segments is not None
                                 else int(env_seg) if env_seg else None)
@@ -488,7 +488,11 @@ class MfSgdGpu(paralg):
         else:
             nseg = self.stream_segments
             if nseg is None:
-                nseg = max(2, min(8, round(self.h_ru.numel() / 64e6)))
+                # two staging buffers of at most 1 GiB each; never fewer than two segments, so that
+                # the copy of one always runs under the kernel of the other
+                compact = self.compact and not self.g8 and self.h_packed is not None
+                stream_bytes = self.h_ru.numel() * (self.packed_bits / 8.0 if compact else 12.0)
+                nseg = max(2, math.ceil(stream_bytes / float(1 << 30)))
             self._sgd_pass_streamed(nseg)
 
     def _sgd_pass_streamed(self, nseg: int):
