@@ -122,18 +122,26 @@ class RoundResult:
     """Result of one ``round()``: the squared pre-update error of its SGD pass.  The 8-byte copy
     to pinned host memory is queued right behind the pass, so ``sse()`` waits for that copy only
     and a caller that keeps one round in flight (queue round t + 1, then read round t) never lets
-    the device run dry while the host reads."""
-    __slots__ = ("_ev", "_host")
+    the device run dry while the host reads.  The model keeps the results of its last four rounds;
+    a handle that is older than that raises instead of returning another round's value."""
+    __slots__ = ("_ev", "_host", "_model", "_no", "_val")
 
-    def __init__(self, ev, host):
-        self._ev, self._host = ev, host
+    def __init__(self, ev, host, model, no):
+        self._ev, self._host, self._model, self._no, self._val = ev, host, model, no, None
 
     def sse(self) -> float:
-        self._ev.synchronize()
-        return float(self._host.item())
+        if self._val is None:
+            if self._model._res_no - self._no >= self._model.RESULT_SLOTS:
+                raise RuntimeError("this round's result slot has been reused: read a RoundResult "
+                                   "within four rounds of the round that returned it")
+            self._ev.synchronize()
+            self._val = float(self._host.item())
+        return self._val
 
 
 class MfSgdGpu(paralg):
+    RESULT_SLOTS = 4      # rounds whose RoundResult stays readable
+
     def __init__(self, n_users: int, n_items: int, k: int = 128, alpha: float = 0.005,
                  beta: float = 0.02, rounds: int = 1, staleness: int = 2, ssp: bool = True,
                  group=None, device=None, seed: int = 0, hot_mix: Optional[float] = None,
@@ -223,8 +231,8 @@ class MfSgdGpu(paralg):
                                 else int(env_seg) if env_seg else None)
         self.sse = torch.zeros(1, dtype=torch.float64, device=self.device)
         # results of the last four rounds in pinned host memory (see RoundResult)
-        self._sse_host = torch.zeros(4, 1, dtype=torch.float64).pin_memory()
-        self._sse_ev = [torch.cuda.Event() for _ in range(4)]
+        self._sse_host = torch.zeros(self.RESULT_SLOTS, 1, dtype=torch.float64).pin_memory()
+        self._sse_ev = [torch.cuda.Event() for _ in range(self.RESULT_SLOTS)]
         self._res_no = 0
         self.host_stream = None
         self.h2d_bytes = 0
@@ -662,11 +670,11 @@ class MfSgdGpu(paralg):
         with self.phase("sgd"):
             self.sse.zero_()
             self.sgd_pass()
-        slot = self._res_no % 4
+        slot = self._res_no % self.RESULT_SLOTS
         self._res_no += 1
         self._sse_host[slot].copy_(self.sse, non_blocking=True)
         self._sse_ev[slot].record()
-        result = RoundResult(self._sse_ev[slot], self._sse_host[slot])
+        result = RoundResult(self._sse_ev[slot], self._sse_host[slot], self, self._res_no)
         if self.overlap_push and self.world > 1 and self.ssp and self.staleness >= 2:
             self._push_overlapped()
         else:

@@ -157,6 +157,35 @@ def test_mf_single_chunk_matches_sequential_oracle():
         m.free()
 
 
+def test_round_result_handles():
+    """round() returns a handle to the pass's squared error: it agrees with the device-side sum
+    when read at once, stays readable while later rounds are queued, and refuses to answer once
+    its slot has been reused."""
+    from paracel_b200.models.mf_gpu import MfSgdGpu
+    from paracel_b200.utils.synth import MfRatingStream
+    dev = "cuda:0"
+    st = MfRatingStream(1500, 400, 20_000, seed=3, device=dev)
+    u, i, r = st.chunk_at(0)
+    m = MfSgdGpu(1500, 400, k=32, rounds=12, device=dev, staleness=0, ssp=False)
+    m.load_ratings(u, i, r)
+    m.init_parameters()
+    first = m.round()
+    assert first.sse() == float(m.sse.item()) and first.sse() > 0
+    held = [m.round() for _ in range(3)]             # three rounds queued, none read yet
+    vals = [h.sse() for h in held]
+    assert all(v > 0 for v in vals) and vals[0] != vals[1]
+    assert vals[-1] == float(m.sse.item())
+    assert vals[-1] < first.sse()                    # the error of the pass goes down
+    old = m.round()
+    for _ in range(MfSgdGpu.RESULT_SLOTS):
+        m.round()
+    with pytest.raises(RuntimeError):
+        old.sse()
+    assert first.sse() > 0                           # a value that was read stays available
+    m.paracel_check()
+    m.free()
+
+
 def test_mf_converges_like_sequential_pass():
     from paracel_b200.models.mf_gpu import MfSgdGpu
     from paracel_b200.utils.synth import MfRatingStream
