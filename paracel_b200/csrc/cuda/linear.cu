@@ -190,6 +190,8 @@ __device__ __forceinline__ void sg_scatter(const SparseGradArgs& a, int* s_hot, 
 // only as many chains in flight as resident warps (long scoreboard 17 stall cycles per issue).
 // Rows of up to 64 non-zeros keep their ids and values in registers between the margin and the
 // scatter; longer rows take the loop form.
+// Measured on 50 M x 2^24 with 40 non-zeros per row: 1 / 2 / 4 / 8 rows per step give 2.04 / 3.16 /
+// 3.36 / 2.06 G samples/s (eight rows cost too many registers).
 __global__ void __launch_bounds__(256) sparse_grad_kernel(SparseGradArgs a) {
   extern __shared__ int s_hot[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
