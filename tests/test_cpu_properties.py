@@ -125,8 +125,11 @@ class _KvModel:
                 cur, uniq = got
                 assert cur == self.d[key]
                 assert kv.cas(key, val, uniq)
-                assert not kv.cas(key, val, uniq)       # the token is spent
-                self.d[key] = val
+                # the version token is a hash of the stored value (as in the reference): it stays
+                # valid exactly when the write did not change the value
+                again = kv.cas(key, val + 1, uniq)
+                assert again == (val == cur)
+                self.d[key] = val + 1 if again else val
             else:
                 assert got is None
 
