@@ -12,7 +12,7 @@ from hypothesis import strategies as st
 from paracel_b200._core import core
 from paracel_b200.utils.packer import pack, unpack
 
-_settings = settings(max_examples=60, deadline=None,
+_settings = settings(max_examples=150, deadline=None, derandomize=True,
                      suppress_health_check=[HealthCheck.function_scoped_fixture, HealthCheck.too_slow])
 
 _scalars = st.one_of(st.booleans(), st.integers(-2 ** 62, 2 ** 62),
