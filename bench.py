@@ -68,7 +68,7 @@ def parse_args():
     ap.add_argument("--heldout", type=int, default=2_000_000,
                     help="pairs drawn like the training pairs but never trained on (0: skip)")
     ap.add_argument("--grid", default="", help="rank grid ROWSxCOLS of the rating partition (default: the "
-                    "most square factorisation)")
+                    "factorisation with the fewest factor rows per rank)")
     ap.add_argument("--overlap-push", type=int, default=-1,
                     help="1: push + commit on a side stream under the next SGD pass; 0: in line; "
                          "-1: the model's default")
@@ -78,8 +78,11 @@ def parse_args():
 def main():
     args = parse_args()
     if args.impl == "reference":
-        from benchmarks.reference_arm import run_reference_arm
-        print(json.dumps(run_reference_arm(args)))
+        # launched like the other arm (one process per GPU under torchrun): the first rank alone
+        # drives the reference's own launcher and prints the line
+        if int(os.environ.get("RANK", "0")) == 0:
+            from benchmarks.reference_arm import run_reference_arm
+            print(json.dumps(run_reference_arm(args)))
         return 0
 
     import torch
