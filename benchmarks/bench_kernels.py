@@ -93,7 +93,7 @@ def bench_gram(flush):
 
 def bench_balltree(flush):
     import numpy as np
-    from paracel_b200.tool.balltree import DeviceBalltree, PyBalltree, search_batch_gpu
+    from paracel_b200.tool.balltree import DeviceBalltree, PyBalltree
     rng = np.random.default_rng(0)
     # clustered items: branch and bound can prune
     centres = rng.standard_normal((200, 64)) * 4
@@ -175,7 +175,7 @@ def bench_spmm(flush):
 def bench_sim_topk(flush):
     """Similarity of 16 k rows against 131 k rows (dim 128) with a running top-20: the 3xTF32
     tcgen05 GEMM + top-k kernel against torch.matmul (fp32) + torch.topk on the same tiles."""
-    from paracel_b200.ops.gemm import gemm_nt, split3
+    from paracel_b200.ops.gemm import split3
     from paracel_b200.ops.misc import RunningTopK
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(3)

@@ -9,7 +9,7 @@ can be a parameter-server value, as in the sparse similarity algorithm.
 from __future__ import annotations
 
 from collections import deque
-from typing import Any, Callable, Dict, Hashable, Iterable, List, Optional, Set, Tuple
+from typing import Any, Callable, Dict, Hashable, Iterable, List, Set, Tuple
 
 import numpy as np
 

@@ -6,7 +6,6 @@ from __future__ import annotations
 import multiprocessing as mp
 import os
 import socket
-import sys
 import traceback
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 

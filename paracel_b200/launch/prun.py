@@ -28,7 +28,7 @@ import time
 from typing import List, Optional
 
 from .._core import core
-from ..utils.types import DEFAULT_PORT, SEPERATOR
+from ..utils.types import SEPERATOR
 from .local import free_port
 
 logger = logging.getLogger("paracelrun")

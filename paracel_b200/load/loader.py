@@ -2,11 +2,11 @@
 include/load/loader.hpp:50-394)."""
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, List, Sequence, Tuple, Union
+from typing import Any, Callable, Dict, List, Sequence, Union
 
 import numpy as np
 
-from ..graph import bigraph, bigraph_continuous, digraph, undirected_graph
+from ..graph import bigraph_continuous
 from ..parallel.comm import Comm
 from ..utils.ext import expand
 from .parser import parser_a

@@ -2,7 +2,7 @@
 (reference: include/load/scheduler.hpp:36-343, src/scheduler.cpp:25-113)."""
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, Hashable, List, Sequence, Tuple
+from typing import Callable, Hashable, List, Sequence, Tuple
 
 import numpy as np
 

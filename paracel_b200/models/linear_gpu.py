@@ -20,7 +20,6 @@ are one-sided reductions into the owners' HBM (``paracel_update``).
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

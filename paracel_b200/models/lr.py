@@ -16,7 +16,6 @@ Unlike the reference, whose LR constructor hard-wires SSP off (lr.cpp:55-56),
 """
 from __future__ import annotations
 
-import math
 from typing import List, Optional, Sequence, Tuple
 
 import numpy as np

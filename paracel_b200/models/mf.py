@@ -9,7 +9,7 @@ The GPU version of the same round structure is ``paracel_b200.models.mf_gpu.MfSg
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Tuple
+from typing import List, Tuple
 
 import numpy as np
 

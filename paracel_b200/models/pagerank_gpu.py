@@ -15,7 +15,6 @@ vertex with out-links."""
 from __future__ import annotations
 
 import os
-from typing import Dict, Optional
 
 import torch
 import torch.distributed as dist

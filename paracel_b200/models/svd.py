@@ -10,7 +10,6 @@ handler, barrier, read), as in svd.hpp:137-181.  Stage 2: Cholesky-QR of W and H
 ``V = Q_H V_r``.  Dumps SIGMA_0, U_<rank>, V_0."""
 from __future__ import annotations
 
-from typing import Dict
 
 import numpy as np
 

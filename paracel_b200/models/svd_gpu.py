@@ -17,10 +17,8 @@ matrices."""
 from __future__ import annotations
 
 import os
-from typing import Optional
 
 import torch
-import torch.distributed as dist
 
 from ..ops.gemm import gemm_nt
 from ..ops.misc import gram

@@ -1,7 +1,6 @@
 """Gradient kernels of the linear models (``csrc/cuda/linear.cu``)."""
 from __future__ import annotations
 
-from typing import Optional, Tuple
 
 import torch
 

@@ -1,10 +1,9 @@
 """Wrappers of the smaller kernels in ``csrc/cuda/misc.cu``."""
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
-import torch.distributed as dist
 
 from . import _lib
 from ..parallel.symm import SymmBuffer

@@ -25,14 +25,12 @@ iterations behind, then pulls and refreshes the cache.
 """
 from __future__ import annotations
 
-import glob
 import heapq
 import os
 import time
 from concurrent.futures import Future
-from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple, Union
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple, Union
 
-from .graph import bigraph, bigraph_continuous, digraph
 from .load.loader import loader
 from .load.parser import parser_a
 from .load.partition import partition

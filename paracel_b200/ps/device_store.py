@@ -21,13 +21,13 @@ belong to the host parameter server (any msgpack value), exactly as before.
 """
 from __future__ import annotations
 
-from typing import Any, Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
 from ..ops import _lib
-from .device_handlers import LINEAR_KINDS, key_filter, resolve_device_handler
+from .device_handlers import key_filter, resolve_device_handler
 from .tables import DenseTable, RowTable, ScalarTable
 
 

@@ -1,7 +1,7 @@
 """Consistent-hash ring over server ids (reference: include/ring.hpp:35-98)."""
 from __future__ import annotations
 
-from typing import Any, Dict, Iterable, List
+from typing import Any, Dict, Iterable
 
 from .._core import core
 

@@ -4,7 +4,6 @@ import sys
 
 from ..parallel.comm import Comm
 from ..paralg import paralg
-from ..utils.misc import json_parser
 
 
 def serial_paralg(output: str) -> paralg:

@@ -18,9 +18,7 @@ from __future__ import annotations
 import json
 import os
 import pickle
-from typing import Any, Dict, Optional
-
-import msgpack
+from typing import Any, Dict
 
 
 def _atomic_write(path: str, data: bytes) -> None:

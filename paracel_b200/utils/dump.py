@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import io
 import os
-from typing import Dict, Iterable, Sequence, Tuple, Union
+from typing import Dict, Sequence, Union
 
 Sink = Union[str, io.TextIOBase]
 

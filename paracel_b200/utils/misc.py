@@ -2,7 +2,6 @@
 from __future__ import annotations
 
 import json
-import os
 import random as _random
 from typing import Any, Callable, Dict, List, Sequence
 

@@ -1,6 +1,5 @@
 """Partitioner, parsers, scheduler placement, graph containers (cases of the reference's
 test_partition.cpp and test_graph.cpp plus the loader paths)."""
-import os
 
 import numpy as np
 import pytest

@@ -4,7 +4,6 @@ import json
 import os
 
 import numpy as np
-import pytest
 
 from paracel_b200.launch.local import LocalJob
 from workers import cpu_workers as W

@@ -2,7 +2,6 @@
 (the reference's local mode: `prun.py -w W -p P -m local`, .travis.yml:87-92).  Covers every
 Comm primitive, the whole parameter-server operation table, SSP (bound, departure, timeout
 by a withheld commit) and the algorithms end to end against NumPy oracles."""
-import math
 import os
 
 import numpy as np

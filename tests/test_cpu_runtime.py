@@ -7,7 +7,6 @@ import sys
 import time
 
 import numpy as np
-import pytest
 
 from paracel_b200.launch.cluster import (FAILED, FINISHED, GangScheduler, LocalAgent, SubmitScheduler,
                                          Task, TaskExecutor)

@@ -2,7 +2,6 @@
 by ``paracel_b200.launch.local.LocalJob``)."""
 from __future__ import annotations
 
-import math
 import time
 
 import torch
@@ -11,7 +10,7 @@ import torch.distributed as dist
 
 def symm_and_rows(comm, server_info):
     from paracel_b200.parallel.symm import SymmBuffer
-    from paracel_b200.ps.tables import RowTable, ScalarTable
+    from paracel_b200.ps.tables import RowTable
     rank, world = comm.get_rank(), comm.get_size()
     dev = torch.device("cuda", torch.cuda.current_device())
     out = {}
