@@ -186,3 +186,36 @@ def test_lines_organize_bins_every_triple_where_h_says(edges, pattern, shape):
     for rank, sl in enumerate(slots):
         for a, b, _ in sl:
             assert sch.h(a, b) == rank
+
+
+@_settings
+@given(st.sampled_from(["", "W_", "usr_bias_", "x"]), st.sampled_from(["", "_pr", "_links"]),
+       st.sets(st.integers(0, 2 ** 40), min_size=1, max_size=30), st.booleans(), st.data())
+def test_key_directory_round_trip(prefix, suffix, ids, with_names, data):
+    """String keys of a device table: ``key_of`` and ``row_of`` invert each other for every row,
+    with and without original-id names; keys of other forms and ids outside the table map to
+    nothing."""
+    import numpy as np
+    import torch
+    from types import SimpleNamespace
+    from paracel_b200.ps.device_store import TableEntry
+    names = np.array(sorted(ids), dtype=np.int64) if with_names else None
+    rows = len(ids) if with_names else data.draw(st.integers(1, 1000))
+    e = TableEntry("rows", SimpleNamespace(rows=rows, width=4, device="cpu"), prefix=prefix, suffix=suffix,
+                   names=names)
+    probe = range(rows) if rows <= 50 else data.draw(st.lists(st.integers(0, rows - 1), min_size=1, max_size=20))
+    for r in probe:
+        k = e.key_of(r)
+        assert k.startswith(prefix) and k.endswith(suffix)
+        assert e.row_of(k) == r
+    # an id that is not in the table
+    outside = (max(ids) + 1) if with_names else rows
+    assert e.row_of(f"{prefix}{outside}{suffix}") is None
+    # another key form
+    assert e.row_of(f"zz{prefix}0{suffix}") is None or prefix == ""
+    if prefix or suffix:
+        assert e.row_of("0") is None
+    # the bulk form agrees with the scalar one
+    if with_names:
+        t = torch.as_tensor(names)
+        assert e.rows_of_ids(t).tolist() == list(range(rows))
