@@ -80,12 +80,24 @@ __device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigne
 constexpr float FX_SCALE = 4194304.f;          // 2^22
 constexpr float FX_INV = 1.f / 4194304.f;
 
+// Layout of a hot row's fixed-point deltas in shared memory.  Lane l of a half-warp owns elements
+// 4 l + j and 64 + 4 l + j (j < 4) of a row; its j-th delta lives at word 16 j + l (64 + 16 j + l
+// for the second group), so the sixteen lanes of one atomic instruction hit sixteen consecutive
+// banks instead of every fourth one (a two-way conflict inside the half-warp and four-way when
+// both halves update hot rows).  Rows are 144 words apart: consecutive rows start sixteen banks
+// apart, so two hot rows of different parity do not collide either.
+constexpr int HDS = 144;
+__device__ __forceinline__ int hd_index(int idx) {   // idx = row * 128 + element
+  const int e = idx & 127;
+  return (idx >> 7) * HDS + (e & 64) + ((e & 3) << 4) + ((e & 63) >> 2);
+}
+
 // current value of a hot row: base + fixed-point delta
 __device__ __forceinline__ Row8 load_hot(const float* base_row, const int* delta_row, int l) {
   const float4 b0 = *reinterpret_cast<const float4*>(base_row + l * 4);
   const float4 b1 = *reinterpret_cast<const float4*>(base_row + 64 + l * 4);
-  const int4 d0 = *reinterpret_cast<const int4*>(delta_row + l * 4);
-  const int4 d1 = *reinterpret_cast<const int4*>(delta_row + 64 + l * 4);
+  const int4 d0 = make_int4(delta_row[l], delta_row[16 + l], delta_row[32 + l], delta_row[48 + l]);
+  const int4 d1 = make_int4(delta_row[64 + l], delta_row[80 + l], delta_row[96 + l], delta_row[112 + l]);
   Row8 r;
   const unsigned long long inv2 = pk2(FX_INV, FX_INV);
   upk2(fma2(pk2((float)d0.x, (float)d0.y), inv2, pk2(b0.x, b0.y)), r.a.x, r.a.y);
@@ -103,18 +115,17 @@ __device__ __forceinline__ void red_global(float* row, int l, const Row8& d) {
 __device__ __forceinline__ int to_fx(float x) { return __float2int_rn(x * FX_SCALE); }
 
 __device__ __forceinline__ void add_hot(int* row, int l, const Row8& d) {
-  int* p = row + l * 4;
+  int* p = row + l;
   const unsigned long long sc2 = pk2(FX_SCALE, FX_SCALE);
   float x0, x1, x2, x3, x4, x5, x6, x7;
   upk2(mul2(pk2(d.a.x, d.a.y), sc2), x0, x1);
   upk2(mul2(pk2(d.a.z, d.a.w), sc2), x2, x3);
   upk2(mul2(pk2(d.b.x, d.b.y), sc2), x4, x5);
   upk2(mul2(pk2(d.b.z, d.b.w), sc2), x6, x7);
-  atomicAdd(p, __float2int_rn(x0)); atomicAdd(p + 1, __float2int_rn(x1));
-  atomicAdd(p + 2, __float2int_rn(x2)); atomicAdd(p + 3, __float2int_rn(x3));
-  p += 64;
-  atomicAdd(p, __float2int_rn(x4)); atomicAdd(p + 1, __float2int_rn(x5));
-  atomicAdd(p + 2, __float2int_rn(x6)); atomicAdd(p + 3, __float2int_rn(x7));
+  atomicAdd(p, __float2int_rn(x0)); atomicAdd(p + 16, __float2int_rn(x1));
+  atomicAdd(p + 32, __float2int_rn(x2)); atomicAdd(p + 48, __float2int_rn(x3));
+  atomicAdd(p + 64, __float2int_rn(x4)); atomicAdd(p + 80, __float2int_rn(x5));
+  atomicAdd(p + 96, __float2int_rn(x6)); atomicAdd(p + 112, __float2int_rn(x7));
 }
 
 __device__ __forceinline__ float dot8(const Row8& x, const Row8& y) {
@@ -157,8 +168,8 @@ __global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
   constexpr int D = 128;
   extern __shared__ float smem[];
   const int T = a.hot_T;
-  int* hd = reinterpret_cast<int*>(smem);                   // T x 128 fixed-point deltas of the period
-  float* hbase = smem + (size_t)T * D;                      // T x 128 values at the start of the period
+  int* hd = reinterpret_cast<int*>(smem);                   // T rows of fixed-point deltas (hd_index)
+  float* hbase = smem + (size_t)T * HDS;                    // T x 128 values at the start of the period
   int* hbd = reinterpret_cast<int*>(hbase + (size_t)T * D); // T bias deltas
   float* hbb = reinterpret_cast<float*>(hbd + T);           // T bias bases
   const int lane = threadIdx.x & 31;
@@ -182,11 +193,12 @@ __global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
       __syncthreads();
       for (int idx = threadIdx.x; idx < T * D; idx += blockDim.x) {
         float* gp = a.H + idx;           // hot rows are the first T rows of H
+        const int hx = hd_index(idx);
         if (it > 0) {
-          const int d = hd[idx];
+          const int d = hd[hx];
           if (d != 0) atomicAdd(gp, (float)d * (FX_INV * (a.hot_fs ? a.hot_fs[idx >> 7] : a.flush_scale)));
         }
-        hd[idx] = 0;
+        hd[hx] = 0;
         hbase[idx] = __ldcg(gp);
       }
       for (int row = threadIdx.x; row < T; row += blockDim.x) {
@@ -285,7 +297,7 @@ __global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
       }
       if (u < 0) continue;   // padding (uniform per half-warp)
       if (hot) {
-        h = load_hot(hbase + i * D, hd + i * D, l);
+        h = load_hot(hbase + i * D, hd + i * HDS, l);
         bi = fmaf((float)hbd[i], FX_INV, hbb[i]);
       }
       if (u != cur_u) {
@@ -316,7 +328,7 @@ __global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
       const float dbi = s_i * (a2e - ab * bi);
       bu += a2e - ab * bu;
       if (hot) {
-        add_hot(hd + i * D, l, dh);
+        add_hot(hd + i * HDS, l, dh);
         if (l == 0) atomicAdd(&hbd[i], to_fx(dbi));
       } else {
         red_global(a.H + (long long)i * D, l, dh);
@@ -335,7 +347,7 @@ __global__ void __launch_bounds__(THREADS, 1) mf_sgd_kernel_h16(MfH16Args a) {
   if (T > 0) {
     __syncthreads();
     for (int idx = threadIdx.x; idx < T * D; idx += blockDim.x) {
-      const int d = hd[idx];
+      const int d = hd[hd_index(idx)];
       if (d != 0) atomicAdd(a.H + idx, (float)d * (FX_INV * (a.hot_fs ? a.hot_fs[idx >> 7] : a.flush_scale)));
     }
     for (int row = threadIdx.x; row < T; row += blockDim.x) {
@@ -384,7 +396,7 @@ PCL_API int pcl_mf_sgd_pass_h16(const int* ru, const int* ri, const float* rr, l
   const long long need = (a.nchunks + per_cta - 1) / per_cta;
   if (need < blocks) blocks = (int)need;
   a.flush_scale = flush_scale > 0.f ? flush_scale : 1.f / (float)blocks;
-  const size_t smem = (size_t)hot_T * (2 * 128 + 2) * sizeof(float);
+  const size_t smem = (size_t)hot_T * (HDS + 128 + 2) * sizeof(float);
   if (smem > 220 * 1024) return (int)cudaErrorInvalidValue;
   cudaError_t e = cudaSuccess;
 #define PCL_H16_LAUNCH(T)                                                                              \

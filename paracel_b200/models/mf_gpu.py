@@ -277,7 +277,7 @@ class MfSgdGpu(paralg):
         if self.g8:
             T = min(T, (220 * 1024) // ((2 * 132 + 2) * 4))
         elif self.h16:
-            T = min(T, (220 * 1024) // ((2 * 128 + 2) * 4))
+            T = min(T, (220 * 1024) // ((144 + 128 + 2) * 4))   # delta rows are 144 words apart
         else:
             T = min(T, (110 * 1024) // ((2 * self.D + 2) * 4))
         self.hot_T = T
